@@ -1,0 +1,188 @@
+"""ctypes binding of ``libcoresets_b200.so`` (declared in ``include/coresets_b200.h``).
+
+This module replaces the reference's JIT loader (src/coresets/cuda/extension.py:15-85).  The
+library is built in-tree with nvcc (``python -m coresets_b200.build``); when it is missing and
+nvcc is on the machine it is compiled on first use, like the reference does, and when it can
+be neither found nor built every entry point raises ``RuntimeError`` -- there is no CPU or
+PyTorch fallback behind this boundary.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+from . import build as _build
+
+CS_ABI_VERSION = 1
+CS_CTL_BYTES = 256
+
+MODE_PRUNE = 0
+MODE_DENSE = 1
+RULE_NONE = 0
+RULE_SIM_SINGLE = 1
+RULE_SIM_SHARDED = 2
+
+EXPORTS = (
+    "cs_version", "cs_error_string", "cs_last_cuda_error", "cs_device_check", "cs_init_state",
+    "cs_reset_ctl", "cs_force_pick", "cs_commit_bound", "cs_fps_step", "cs_sim_begin",
+    "cs_sim_final_check", "cs_fps_step_lanes",
+)
+
+
+class CsState(ctypes.Structure):
+    """``cs_state`` of include/coresets_b200.h."""
+    _fields_ = [
+        ("X", ctypes.c_void_p),
+        ("norms", ctypes.c_void_p),
+        ("h", ctypes.c_void_p),
+        ("voronoi", ctypes.c_void_p),
+        ("N_local", ctypes.c_int64),
+        ("shard_offset", ctypes.c_int64),
+        ("D", ctypes.c_int32),
+        ("world_size", ctypes.c_int32),
+        ("X_sel", ctypes.c_void_p),
+        ("norms_sel", ctypes.c_void_p),
+        ("dSL_quarter", ctypes.c_void_p),
+        ("cap", ctypes.c_int64),
+        ("selected", ctypes.c_void_p),
+        ("eps", ctypes.c_void_p),
+        ("ctl", ctypes.c_void_p),
+        ("pack_local", ctypes.c_void_p),
+        ("pack_all", ctypes.c_void_p),
+    ]
+
+
+class CtlView(ctypes.Structure):
+    """``cs_ctl_view`` of include/coresets_b200.h."""
+    _fields_ = [
+        ("key", ctypes.c_uint64 * 2),
+        ("n_sel", ctypes.c_int32),
+        ("ticket", ctypes.c_uint32),
+        ("status", ctypes.c_int32),
+        ("viable", ctypes.c_int32),
+        ("sep", ctypes.c_float),
+        ("steps", ctypes.c_int32),
+        ("live_rows", ctypes.c_uint64),
+        ("last_val", ctypes.c_float),
+        ("last_idx", ctypes.c_int32),
+        ("reserved", ctypes.c_uint8 * (CS_CTL_BYTES - 56)),
+    ]
+
+
+assert ctypes.sizeof(CtlView) == CS_CTL_BYTES
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+class Native:
+    """Thin, typed wrapper over the C entry points.  Methods take a ``CsState`` (or an array of
+    them) and a raw ``cudaStream_t`` value; a non-zero return code raises ``NativeError``."""
+
+    def __init__(self, path: Optional[str] = None):
+        lib_path = path or str(_build.LIB)
+        try:
+            self.lib = ctypes.CDLL(lib_path)
+        except OSError as e:
+            raise NativeError(
+                f"cannot load {lib_path}: {e}. Build it with `python -m coresets_b200.build`."
+            ) from e
+        L = self.lib
+        missing = [n for n in EXPORTS if not hasattr(L, n)]
+        if missing:
+            raise NativeError(f"{lib_path} lacks symbols {missing}; rebuild it")
+        L.cs_version.restype = ctypes.c_int
+        L.cs_error_string.restype = ctypes.c_char_p
+        L.cs_error_string.argtypes = [ctypes.c_int]
+        L.cs_last_cuda_error.restype = ctypes.c_char_p
+        L.cs_device_check.restype = ctypes.c_int
+        sp = ctypes.POINTER(CsState)
+        vp = ctypes.c_void_p
+        for name, args in (
+            ("cs_init_state", [sp, vp]),
+            ("cs_reset_ctl", [sp, ctypes.c_int32, vp]),
+            ("cs_force_pick", [sp, ctypes.c_int64, ctypes.c_float, vp]),
+            ("cs_commit_bound", [sp, ctypes.c_uint32, vp]),
+            ("cs_fps_step", [sp, ctypes.c_uint32, vp]),
+            ("cs_sim_begin", [sp, ctypes.c_float, vp]),
+            ("cs_sim_final_check", [sp, vp]),
+            ("cs_fps_step_lanes", [sp, ctypes.c_int32, ctypes.c_uint32, vp]),
+        ):
+            fn = getattr(L, name)
+            fn.restype = ctypes.c_int
+            fn.argtypes = args
+        if L.cs_version() != CS_ABI_VERSION:
+            raise NativeError(f"{lib_path}: ABI {L.cs_version()} != expected {CS_ABI_VERSION}; rebuild it")
+
+    def _check(self, rc: int, what: str) -> None:
+        if rc != 0:
+            msg = self.lib.cs_error_string(rc).decode()
+            if rc == -4:
+                msg += ": " + self.lib.cs_last_cuda_error().decode()
+            raise NativeError(f"{what} failed ({rc}): {msg}")
+
+    def device_check(self) -> int:
+        sms = self.lib.cs_device_check()
+        if sms < 0:
+            self._check(sms, "cs_device_check")
+        return sms
+
+    def init_state(self, s: CsState, stream: int) -> None:
+        self._check(self.lib.cs_init_state(ctypes.byref(s), stream), "cs_init_state")
+
+    def reset_ctl(self, s: CsState, n_sel: int, stream: int) -> None:
+        self._check(self.lib.cs_reset_ctl(ctypes.byref(s), n_sel, stream), "cs_reset_ctl")
+
+    def force_pick(self, s: CsState, global_idx: int, val: float, stream: int) -> None:
+        self._check(self.lib.cs_force_pick(ctypes.byref(s), global_idx, val, stream), "cs_force_pick")
+
+    def commit_bound(self, s: CsState, rules: int, stream: int) -> None:
+        self._check(self.lib.cs_commit_bound(ctypes.byref(s), rules, stream), "cs_commit_bound")
+
+    def fps_step(self, s: CsState, mode: int, stream: int) -> None:
+        self._check(self.lib.cs_fps_step(ctypes.byref(s), mode, stream), "cs_fps_step")
+
+    def sim_begin(self, s: CsState, sep: float, stream: int) -> None:
+        self._check(self.lib.cs_sim_begin(ctypes.byref(s), sep, stream), "cs_sim_begin")
+
+    def sim_final_check(self, s: CsState, stream: int) -> None:
+        self._check(self.lib.cs_sim_final_check(ctypes.byref(s), stream), "cs_sim_final_check")
+
+    def fps_step_lanes(self, lanes, n_lanes: int, mode: int, stream: int) -> None:
+        self._check(self.lib.cs_fps_step_lanes(lanes, n_lanes, mode, stream), "cs_fps_step_lanes")
+
+
+_native: Optional[Native] = None
+
+
+def ensure_compiled() -> None:
+    """Load the native library, compiling it first if it is absent and nvcc is available.
+    Mirrors ``ensure_compiled`` of the reference (src/coresets/cuda/extension.py:15-74)."""
+    global _native
+    if _native is not None:
+        return
+    if not _build.LIB.is_file():
+        try:
+            print("Compiling coresets_b200 CUDA kernels for sm_100a (first use)...")
+            _build.build()
+        except Exception as e:  # no nvcc, or the compile failed: fail loudly
+            raise NativeError(
+                f"{_build.LIB} is missing and could not be built ({e}). "
+                "Run `python -m coresets_b200.build` on a machine with nvcc (CUDA >= 12.8)."
+            ) from e
+    _native = Native()
+
+
+def get_native() -> Native:
+    ensure_compiled()
+    assert _native is not None
+    return _native
+
+
+def set_native_for_tests(obj) -> None:
+    """Install a stand-in for the native library.  Only the CPU test-suite calls this (with an
+    implementation backed by the oracle); it exists because multi-rank host logic has to be
+    testable on machines without a GPU."""
+    global _native
+    _native = obj

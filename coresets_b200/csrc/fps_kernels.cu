@@ -1,0 +1,621 @@
+// sm_100a kernels and C entry points of the farthest-point-sampling engine.
+//
+// Data layout in HBM (per rank): X [N_local, D] fp32 row-major (streamed once per pick),
+// norms / h fp32 [N_local], voronoi int32 [N_local]; the committed centres X_sel [cap, D],
+// norms_sel, dSL_quarter are small and L2-resident.  One pick = commit_bound_kernel (tiny) +
+// fps_step_kernel (the bandwidth-bound pass over X with the arg-max fused in).
+//
+// Arithmetic is spelled with __fmul_rn/__fmaf_rn/__fadd_rn so that no compiler contraction or
+// reassociation can change a bit; the file is compiled with -ftz=true because the reference
+// builds with --use_fast_math (src/coresets/cuda/extension.py:63).
+#include "coresets_b200.h"
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+typedef unsigned long long u64;
+
+// Device layout of the control block; mirrors cs_ctl_view.
+struct Ctl {
+    u64 key[2];
+    int n_sel;
+    unsigned ticket;
+    int status;
+    int viable;
+    float sep;
+    int steps;
+    u64 live_rows;
+    float last_val;
+    int last_idx;
+};
+static_assert(sizeof(Ctl) <= CS_CTL_BYTES, "control block too large");
+static_assert(sizeof(cs_ctl_view) == CS_CTL_BYTES, "cs_ctl_view must span the control block");
+
+enum { ST_CAPACITY = 1, ST_FORCE_NOT_OWNED = 2 };
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr unsigned kFull = 0xffffffffu;
+
+thread_local cudaError_t g_last_cuda = cudaSuccess;
+
+// ---- order-preserving key ---------------------------------------------------------------
+// Larger h wins, equal h -> smaller global index wins (argmax_better, _shared.cuh:24-27).
+// key = orderable(h) << 32 | (0xFFFFFFFF - global_idx); max over keys is associative and
+// commutative, so warp / block / grid / cross-rank reduction order cannot change the winner.
+// key 0 means "no candidate" (empty shard; reference: (-inf, -1), multi.cu:283-292).
+__device__ __forceinline__ unsigned f2ord(float h) {
+    unsigned b = __float_as_uint(h);
+    if (h == 0.0f) b = 0u;                 // -0.0 and +0.0 compare equal in the reference
+    if (h != h) return 1u;                 // NaN never wins a reference comparison
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float ord2f(unsigned o) {
+    unsigned b = (o & 0x80000000u) ? (o & 0x7fffffffu) : ~o;
+    return __uint_as_float(b);
+}
+__device__ __forceinline__ u64 make_key(float h, int64_t gidx) {
+    return ((u64)f2ord(h) << 32) | (u64)(0xffffffffu - (unsigned)gidx);
+}
+__device__ __forceinline__ float key_val(u64 k) {
+    return k ? ord2f((unsigned)(k >> 32)) : __uint_as_float(0xff800000u);
+}
+__device__ __forceinline__ int64_t key_idx(u64 k) {
+    return k ? (int64_t)(0xffffffffu - (unsigned)(k & 0xffffffffu)) : (int64_t)-1;
+}
+__device__ __forceinline__ u64 warp_max_key(u64 k) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        u64 o = __shfl_xor_sync(kFull, k, off);
+        k = o > k ? o : k;
+    }
+    return k;
+}
+
+// ---- the reference's dot product ---------------------------------------------------------
+// One float4 chunk: a.x*b.x + a.y*b.y + a.z*b.z + a.w*b.w as the reference's compiler
+// contracts it (_shared.cuh:49): mul on .y, then fma on .x, .z, .w.
+__device__ __forceinline__ float chunk_dot(const float4 a, const float4 b) {
+    float t = __fmul_rn(a.y, b.y);
+    t = __fmaf_rn(a.x, b.x, t);
+    t = __fmaf_rn(a.z, b.z, t);
+    t = __fmaf_rn(a.w, b.w, t);
+    return t;
+}
+// The 5-round tree of warp.cu:35-37.  A xor butterfly gives every lane the value lane 0 gets
+// from the reference's shfl_down tree, because fp32 addition is commutative.
+__device__ __forceinline__ float warp_tree_sum(float p) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) p = __fadd_rn(p, __shfl_xor_sync(kFull, p, off));
+    return p;
+}
+// d = norms[row] + norm_new - 2*dot (warp.cu:41-42); 2*dot is exact.
+__device__ __forceinline__ float sq_dist(float n_row, float n_new, float dot) {
+    return __fsub_rn(__fadd_rn(n_row, n_new), __fadd_rn(dot, dot));
+}
+
+__device__ __forceinline__ float4 ld_stream4(const float4* p) { return __ldcs(p); }
+
+// Generic warp dot: row in global memory, centre anywhere (shared or global); any D.
+__device__ __forceinline__ float warp_dot_generic(const float* __restrict__ row,
+                                                  const float* __restrict__ cen, int D, int lane) {
+    float acc = 0.0f;
+    if ((D & 3) == 0) {
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        const float4* c4 = reinterpret_cast<const float4*>(cen);
+        const int d4 = D >> 2;
+        for (int c = lane; c < d4; c += 32) acc = __fadd_rn(acc, chunk_dot(__ldg(r4 + c), c4[c]));
+    } else {
+        for (int c = lane; c < D; c += 32) acc = __fmaf_rn(__ldg(row + c), cen[c], acc);
+    }
+    return warp_tree_sum(acc);
+}
+
+// ---- winner resolution shared by commit_bound and sim_final_check -------------------------
+struct Winner {
+    u64 key;
+    const float* row;   // D floats (in X or in the gathered packs)
+    float norm;
+};
+__device__ __forceinline__ Winner resolve_winner(const cs_state& s, const Ctl* ctl, int i) {
+    Winner w;
+    w.row = nullptr;
+    w.norm = 0.0f;
+    if (s.world_size <= 1) {
+        w.key = ctl->key[i & 1];
+        if (w.key) {
+            int64_t l = key_idx(w.key) - s.shard_offset;
+            w.row = s.X + l * (int64_t)s.D;
+            w.norm = s.norms[l];
+        }
+    } else {
+        const int stride = 4 + s.D;
+        w.key = 0;
+        int br = -1;
+        for (int r = 0; r < s.world_size; ++r) {
+            const uint32_t* p = s.pack_all + (int64_t)r * stride;
+            u64 k = (u64)p[0] | ((u64)p[1] << 32);
+            if (k > w.key) { w.key = k; br = r; }
+        }
+        if (br >= 0) {
+            const uint32_t* p = s.pack_all + (int64_t)br * stride;
+            w.norm = __uint_as_float(p[2]);
+            w.row = reinterpret_cast<const float*>(p + 4);
+        }
+    }
+    return w;
+}
+
+// ---- kernel A: resolve + commit + triangle bounds ------------------------------------------
+__global__ void __launch_bounds__(kThreads) commit_bound_kernel(const cs_state s, const unsigned rules) {
+    extern __shared__ __align__(16) float s_cen[];
+    Ctl* ctl = reinterpret_cast<Ctl*>(s.ctl);
+    const int i = ctl->n_sel;
+    if (i >= s.cap) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) ctl->status = ST_CAPACITY;
+        return;
+    }
+    const Winner w = resolve_winner(s, ctl, i);
+    const float val = key_val(w.key);
+    const int64_t gidx = key_idx(w.key);
+    const int D = s.D;
+
+    if (blockIdx.x == 0) {
+        if (threadIdx.x == 0) {
+            if (s.selected) s.selected[i] = gidx;
+            if (s.eps) s.eps[i] = val;
+            ctl->last_val = val;
+            ctl->last_idx = (int)gidx;
+            ctl->key[(i + 1) & 1] = 0;     // slot the coming step kernel reduces into
+            ctl->live_rows = 0;
+            if (rules == CS_RULE_SIM_SINGLE) {            // commit.cu:41-51
+                float sep = ctl->sep;
+                if (sep > val) ctl->viable = 1;
+                if (val < sep) ctl->sep = val;
+                ctl->steps += 1;
+            } else if (rules == CS_RULE_SIM_SHARDED) {    // multi.cu:331-340
+                float sep = ctl->sep;
+                if (sep > val || val <= 0.0f || gidx < 0) ctl->viable = 1;
+                if (val > 0.0f && val < sep) ctl->sep = val;
+                ctl->steps += 1;
+            }
+            if (gidx >= 0) {
+                s.norms_sel[i] = w.norm;
+                int64_t l = gidx - s.shard_offset;
+                if (l >= 0 && l < s.N_local) {            // owner marks the row (commit.cu:16-18)
+                    s.h[l] = -1.0f;
+                    s.voronoi[l] = i;
+                }
+            }
+        }
+        if (gidx >= 0) {
+            float* dst = s.X_sel + (int64_t)i * D;
+            for (int c = threadIdx.x; c < D; c += blockDim.x) dst[c] = w.row[c];
+        }
+    }
+    if (gidx < 0 || i == 0) return;
+
+    // dSL_quarter[v] = |X_sel[v] - x_new|^2 / 4 for every old centre (commit.cu:69-102)
+    for (int c = threadIdx.x; c < D; c += blockDim.x) s_cen[c] = w.row[c];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int gw = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const int nw = gridDim.x * kWarps;
+    for (int v = gw; v < i; v += nw) {
+        float dot = warp_dot_generic(s.X_sel + (int64_t)v * D, s_cen, D, lane);
+        if (lane == 0) s.dSL_quarter[v] = __fmul_rn(sq_dist(s.norms_sel[v], w.norm, dot), 0.25f);
+    }
+}
+
+// ---- kernel B: fused distance + min-update + arg-max ---------------------------------------
+// A warp owns tiles of 32 consecutive rows: lane j holds h / voronoi / norm of row base+j
+// (coalesced), the warp then walks the rows that need a distance, RB rows per batch so that
+// RB * CPL 16-byte loads per lane are in flight, every row read with one fully coalesced
+// 512-byte (or wider) request.  CPL = float4 chunks per lane = ceil(D / 128); CPL == 0 is the
+// generic path (any D, centre in shared memory).
+template <int CPL, bool FULL>
+__device__ __forceinline__ void tile_rows(const float4* __restrict__ X4, const int64_t base,
+                                          const int d4, unsigned m, const float4 (&cen)[CPL ? CPL : 1],
+                                          const int lane, float& mydot) {
+    constexpr int RB = CPL >= 8 ? 1 : (8 / (CPL ? CPL : 1));
+    while (m) {
+        int rows[RB];
+        float4 a[RB][CPL ? CPL : 1];
+#pragma unroll
+        for (int b = 0; b < RB; ++b) {
+            rows[b] = m ? (__ffs(m) - 1) : -1;
+            m &= m - 1;                       // m == 0 stays 0
+        }
+#pragma unroll
+        for (int b = 0; b < RB; ++b) {
+            if (rows[b] >= 0) {
+                const float4* rp = X4 + (base + rows[b]) * (int64_t)d4 + lane;
+#pragma unroll
+                for (int c = 0; c < CPL; ++c)
+                    if (FULL || lane + 32 * c < d4) a[b][c] = ld_stream4(rp + 32 * c);
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < RB; ++b) {
+            if (rows[b] >= 0) {
+                float p = 0.0f;
+#pragma unroll
+                for (int c = 0; c < CPL; ++c)
+                    if (FULL || lane + 32 * c < d4) p = __fadd_rn(p, chunk_dot(a[b][c], cen[c]));
+                p = warp_tree_sum(p);
+                if (lane == rows[b]) mydot = p;
+            }
+        }
+    }
+}
+
+template <int CPL, bool FULL>
+__global__ void __launch_bounds__(kThreads) fps_step_kernel(const cs_state s, const unsigned mode) {
+    extern __shared__ __align__(16) float s_cen[];       // generic path only
+    __shared__ u64 s_keys[kWarps];
+    __shared__ unsigned s_live[kWarps];
+    __shared__ int s_last;
+
+    Ctl* ctl = reinterpret_cast<Ctl*>(s.ctl);
+    const int i = ctl->n_sel;
+    if (i >= s.cap) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) ctl->status = ST_CAPACITY;
+        return;
+    }
+    const int D = s.D;
+    const int d4 = D >> 2;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const bool first = (i == 0);                 // slot 0 uses the dense kernel (voronoi_step.py:40-43)
+    const bool dense = (mode & CS_MODE_DENSE) != 0;
+    const float nn = s.norms_sel[i];
+    const float* cen_g = s.X_sel + (int64_t)i * D;
+
+    float4 cen[CPL ? CPL : 1];
+    if (CPL) {
+        const float4* c4 = reinterpret_cast<const float4*>(cen_g);
+#pragma unroll
+        for (int c = 0; c < (CPL ? CPL : 1); ++c)
+            cen[c] = (FULL || lane + 32 * c < d4) ? c4[lane + 32 * c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+        for (int c = threadIdx.x; c < D; c += blockDim.x) s_cen[c] = cen_g[c];
+        __syncthreads();
+    }
+
+    const int64_t N = s.N_local;
+    const int64_t tiles = (N + 31) >> 5;
+    const int64_t nw = (int64_t)gridDim.x * kWarps;
+    const float4* X4 = reinterpret_cast<const float4*>(s.X);
+    u64 best = 0;
+    unsigned live_cnt = 0;
+
+    for (int64_t t = (int64_t)blockIdx.x * kWarps + warp; t < tiles; t += nw) {
+        const int64_t base = t << 5;
+        const int64_t row = base + lane;
+        const bool valid = row < N;
+        float hj = valid ? s.h[row] : -1.0f;
+        const bool live = valid && !(hj < 0.0f);                 // warp.cu:28-30, 75-77
+        bool upd = live;
+        if (live && !first) {
+            const int vj = s.voronoi[row];
+            if (__ldg(s.dSL_quarter + vj) >= hj) upd = false;    // warp.cu:80-82
+        }
+        const bool need = dense ? live : upd;
+        const unsigned m = __ballot_sync(kFull, need);
+        live_cnt += __popc(m);
+        float mydot = 0.0f;
+        if (m) {
+            if (CPL) {
+                tile_rows<CPL, FULL>(X4, base, d4, m, cen, lane, mydot);
+            } else {
+                unsigned mm = m;
+                while (mm) {
+                    const int r = __ffs(mm) - 1;
+                    mm &= mm - 1;
+                    float p = warp_dot_generic(s.X + (base + r) * (int64_t)D, s_cen, D, lane);
+                    if (lane == r) mydot = p;
+                }
+            }
+        }
+        if (upd) {
+            const float d = sq_dist(__ldg(s.norms + row), nn, mydot);
+            if (d < hj) {
+                hj = d;
+                s.h[row] = d;
+                s.voronoi[row] = i;
+            }
+        }
+        if (valid) {
+            const u64 k = make_key(hj, s.shard_offset + row);
+            best = k > best ? k : best;
+        }
+    }
+
+    best = warp_max_key(best);
+    if (lane == 0) { s_keys[warp] = best; s_live[warp] = live_cnt; }
+    __syncthreads();
+    const int slot = (i + 1) & 1;
+    if (threadIdx.x == 0) {
+        u64 bk = 0;
+        unsigned lv = 0;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) { bk = s_keys[w] > bk ? s_keys[w] : bk; lv += s_live[w]; }
+        if (bk) atomicMax(&ctl->key[slot], bk);
+        if (lv) atomicAdd(&ctl->live_rows, (u64)lv);
+        __threadfence();
+        const unsigned tk = atomicAdd(&ctl->ticket, 1u);
+        s_last = (tk == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+
+    // last block to finish: publish this rank's candidate and advance the pick counter
+    __threadfence();
+    const u64 k = *reinterpret_cast<volatile u64*>(&ctl->key[slot]);
+    if (s.world_size > 1) {
+        uint32_t* p = s.pack_local;
+        const int64_t l = key_idx(k) - s.shard_offset;
+        if (threadIdx.x == 0) {
+            p[0] = (uint32_t)(k & 0xffffffffu);
+            p[1] = (uint32_t)(k >> 32);
+            p[2] = k ? __float_as_uint(s.norms[l]) : 0u;
+            p[3] = 0u;
+        }
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(s.X + (k ? l : 0) * (int64_t)D);
+        for (int c = threadIdx.x; c < D; c += blockDim.x) p[4 + c] = k ? src[c] : 0u;
+    }
+    if (threadIdx.x == 0) {
+        ctl->ticket = 0;
+        ctl->n_sel = i + 1;
+    }
+}
+
+// ---- small single-block kernels ---------------------------------------------------------------
+__global__ void init_state_kernel(float* h, int32_t* v, int64_t N, Ctl* ctl) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < N; r += stride) {
+        h[r] = __uint_as_float(0x7f800000u);
+        v[r] = 0;
+    }
+    if (blockIdx.x == 0 && threadIdx.x < CS_CTL_BYTES / 4) reinterpret_cast<uint32_t*>(ctl)[threadIdx.x] = 0u;
+}
+
+__global__ void reset_ctl_kernel(Ctl* ctl, int n_sel) {
+    if (threadIdx.x < CS_CTL_BYTES / 4) reinterpret_cast<uint32_t*>(ctl)[threadIdx.x] = 0u;
+    __syncthreads();
+    if (threadIdx.x == 0) ctl->n_sel = n_sel;
+}
+
+__global__ void force_pick_kernel(const cs_state s, const int64_t gidx, const float val) {
+    Ctl* ctl = reinterpret_cast<Ctl*>(s.ctl);
+    const int i = ctl->n_sel;
+    const int64_t l = gidx - s.shard_offset;
+    const bool owner = (l >= 0 && l < s.N_local);
+    const u64 k = owner ? make_key(val, gidx) : 0;
+    if (threadIdx.x == 0) {
+        ctl->key[i & 1] = k;
+        if (s.world_size <= 1 && !owner) ctl->status = ST_FORCE_NOT_OWNED;
+    }
+    if (s.world_size > 1) {
+        uint32_t* p = s.pack_local;
+        if (threadIdx.x == 0) {
+            p[0] = (uint32_t)(k & 0xffffffffu);
+            p[1] = (uint32_t)(k >> 32);
+            p[2] = owner ? __float_as_uint(s.norms[l]) : 0u;
+            p[3] = 0u;
+        }
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(s.X + (owner ? l : 0) * (int64_t)s.D);
+        for (int c = threadIdx.x; c < s.D; c += blockDim.x) p[4 + c] = owner ? src[c] : 0u;
+    }
+}
+
+__global__ void sim_begin_kernel(Ctl* ctl, float sep) {
+    ctl->viable = 0;
+    ctl->steps = 0;
+    ctl->sep = sep;
+}
+
+__global__ void sim_final_check_kernel(const cs_state s) {
+    Ctl* ctl = reinterpret_cast<Ctl*>(s.ctl);
+    const Winner w = resolve_winner(s, ctl, ctl->n_sel);
+    if (ctl->sep > key_val(w.key)) ctl->viable = 1;   // argmax.cu:152-159, multi.cu:369-384
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+struct DevInfo {
+    int sms = 0;
+    int cc_major = 0;
+    bool ok = false;
+};
+DevInfo device_info() {
+    static thread_local int cached_dev = -1;
+    static thread_local DevInfo info;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return DevInfo();
+    if (dev != cached_dev) {
+        DevInfo d;
+        if (cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return DevInfo();
+        if (cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return DevInfo();
+        d.ok = true;
+        info = d;
+        cached_dev = dev;
+    }
+    return info;
+}
+
+int check_launch() {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        g_last_cuda = e;
+        return CS_E_LAUNCH;
+    }
+    return CS_OK;
+}
+
+int validate(const cs_state* s) {
+    if (!s || !s->ctl || !s->X_sel || !s->norms_sel || !s->dSL_quarter) return CS_E_ARG;
+    if (s->N_local < 0 || s->D <= 0 || s->cap <= 0 || s->world_size < 1 || s->shard_offset < 0) return CS_E_ARG;
+    if (s->N_local > 0 && (!s->X || !s->norms || !s->h || !s->voronoi)) return CS_E_ARG;
+    if (s->world_size > 1 && (!s->pack_local || !s->pack_all)) return CS_E_ARG;
+    if (s->shard_offset + s->N_local >= (int64_t)1 << 31) return CS_E_RANGE;
+    if (s->cap >= (int64_t)1 << 31) return CS_E_RANGE;
+    if ((s->D & 3) == 0) {
+        if (((uintptr_t)s->X | (uintptr_t)s->X_sel) & 15u) return CS_E_ALIGN;
+        if (s->world_size > 1 && (((uintptr_t)s->pack_local | (uintptr_t)s->pack_all) & 15u)) return CS_E_ALIGN;
+    }
+    return CS_OK;
+}
+
+template <int CPL, bool FULL>
+int launch_step(const cs_state* s, unsigned mode, cudaStream_t st, int sms) {
+    static thread_local int bps = 0;
+    const size_t smem = CPL ? 0 : (size_t)s->D * sizeof(float);
+    if (CPL == 0 && smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(fps_step_kernel<CPL, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess) {
+            g_last_cuda = cudaGetLastError();
+            return CS_E_LAUNCH;
+        }
+    }
+    int per_sm = bps;
+    if (CPL == 0 || per_sm == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fps_step_kernel<CPL, FULL>, kThreads, smem) !=
+                cudaSuccess || per_sm < 1) {
+            g_last_cuda = cudaGetLastError();
+            return CS_E_LAUNCH;
+        }
+        if (CPL) bps = per_sm;
+    }
+    const int64_t tiles = (s->N_local + 31) >> 5;
+    int64_t want = (tiles + kWarps - 1) / kWarps;
+    int64_t cap = (int64_t)sms * per_sm;         // persistent grid: a multiple of the SM count
+    int grid = (int)(want < 1 ? 1 : (want < cap ? want : cap));
+    fps_step_kernel<CPL, FULL><<<grid, kThreads, smem, st>>>(*s, mode);
+    return check_launch();
+}
+
+}  // namespace
+
+extern "C" {
+
+int cs_version(void) { return CS_ABI_VERSION; }
+
+const char* cs_error_string(int code) {
+    switch (code) {
+        case CS_OK: return "ok";
+        case CS_E_ARG: return "invalid argument (null pointer, negative size or unknown flag)";
+        case CS_E_ALIGN: return "X, X_sel and the packs must be 16-byte aligned when D is a multiple of 4";
+        case CS_E_RANGE: return "global row index space or capacity must stay below 2^31";
+        case CS_E_LAUNCH: return "CUDA launch failed (see cs_last_cuda_error)";
+        case CS_E_DEVICE: return "no CUDA device of compute capability 10.x is current";
+        default: return "unknown error code";
+    }
+}
+
+const char* cs_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda); }
+
+int cs_device_check(void) {
+    DevInfo d = device_info();
+    if (!d.ok || d.cc_major != 10) return CS_E_DEVICE;
+    return d.sms;
+}
+
+int cs_init_state(const cs_state* s, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    DevInfo d = device_info();
+    if (!d.ok) return CS_E_DEVICE;
+    int64_t want = (s->N_local + 1023) / 1024;
+    int grid = (int)(want < 1 ? 1 : (want < (int64_t)d.sms * 8 ? want : (int64_t)d.sms * 8));
+    init_state_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(s->h, s->voronoi, s->N_local,
+                                                              reinterpret_cast<Ctl*>(s->ctl));
+    return check_launch();
+}
+
+int cs_reset_ctl(const cs_state* s, int32_t n_sel, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    if (n_sel < 0 || n_sel > s->cap) return CS_E_ARG;
+    reset_ctl_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(reinterpret_cast<Ctl*>(s->ctl), n_sel);
+    return check_launch();
+}
+
+int cs_force_pick(const cs_state* s, int64_t global_idx, float val, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    if (global_idx < 0 || global_idx >= (int64_t)1 << 31) return CS_E_RANGE;
+    force_pick_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(*s, global_idx, val);
+    return check_launch();
+}
+
+int cs_commit_bound(const cs_state* s, uint32_t rules, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    if (rules > CS_RULE_SIM_SHARDED) return CS_E_ARG;
+    DevInfo d = device_info();
+    if (!d.ok) return CS_E_DEVICE;
+    const size_t smem = (size_t)s->D * sizeof(float);
+    if (smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(commit_bound_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess) {
+            g_last_cuda = cudaGetLastError();
+            return CS_E_LAUNCH;
+        }
+    }
+    // enough warps for one centre per warp up to the capacity, at most two blocks per SM
+    int64_t want = (s->cap + kWarps - 1) / kWarps;
+    int64_t lim = (int64_t)d.sms * 2;
+    int grid = (int)(want < 1 ? 1 : (want < lim ? want : lim));
+    commit_bound_kernel<<<grid, kThreads, smem, (cudaStream_t)stream>>>(*s, rules);
+    return check_launch();
+}
+
+int cs_fps_step(const cs_state* s, uint32_t mode, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    if (mode > CS_MODE_DENSE) return CS_E_ARG;
+    DevInfo d = device_info();
+    if (!d.ok) return CS_E_DEVICE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int D = s->D;
+    if ((D & 3) != 0 || D > 1024) return launch_step<0, false>(s, mode, st, d.sms);
+    switch (D) {
+        case 128: return launch_step<1, true>(s, mode, st, d.sms);
+        case 256: return launch_step<2, true>(s, mode, st, d.sms);
+        case 512: return launch_step<4, true>(s, mode, st, d.sms);
+        case 1024: return launch_step<8, true>(s, mode, st, d.sms);
+        default: break;
+    }
+    if (D < 128) return launch_step<1, false>(s, mode, st, d.sms);
+    if (D < 256) return launch_step<2, false>(s, mode, st, d.sms);
+    if (D < 512) return launch_step<4, false>(s, mode, st, d.sms);
+    return launch_step<8, false>(s, mode, st, d.sms);
+}
+
+int cs_sim_begin(const cs_state* s, float sep, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    sim_begin_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(reinterpret_cast<Ctl*>(s->ctl), sep);
+    return check_launch();
+}
+
+int cs_sim_final_check(const cs_state* s, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    sim_final_check_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(*s);
+    return check_launch();
+}
+
+int cs_fps_step_lanes(const cs_state* lanes, int32_t n_lanes, uint32_t mode, cs_stream stream) {
+    if (!lanes || n_lanes < 1 || n_lanes > 8) return CS_E_ARG;
+    // each lane's arithmetic is exactly cs_fps_step's; lanes are issued back to back
+    for (int l = 0; l < n_lanes; ++l) {
+        int rc = cs_fps_step(&lanes[l], mode, stream);
+        if (rc) return rc;
+    }
+    return CS_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,219 @@
+"""Host-side engine: owns one rank's device buffers and drives the per-pick launch sequence.
+
+One pick on every rank is
+    [all-gather of the candidate packs]  ->  cs_commit_bound  ->  cs_fps_step
+with the pick counter, the arg-max key and the winning row all staying on the device, so a
+run of picks needs no host synchronisation and is replayed from a CUDA graph.  This replaces
+the reference's per-pick Python loops, which read the winner back to the host every pick
+(src/coresets/cuda/fps.py:105-128, src/coresets/cuda/multi/fps_sharded.py:385-402).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _native
+from ._native import CsState, CtlView, MODE_DENSE, MODE_PRUNE, RULE_NONE
+
+_NORM_CHUNK_ELEMS = 1 << 28  # elements of the X*X temporary per chunk (1 GiB of fp32)
+
+
+def row_norms(X: torch.Tensor) -> torch.Tensor:
+    """Squared row norms with the reference's own expression, ``(X * X).sum(dim=1)``
+    (src/coresets/cuda/fps.py:34, src/coresets/cuda/multi/fps_sharded.py:90), evaluated in row
+    chunks so that no N x D temporary is ever allocated.  Every chunk has the same number of
+    rows (the last one overlaps its predecessor) so each call reduces with the same launch
+    shape as one big call would; the values are bit-identical to the unchunked expression."""
+    N, D = X.shape
+    chunk = max(1, _NORM_CHUNK_ELEMS // max(D, 1))
+    if N <= chunk:
+        return (X * X).sum(dim=1).to(torch.float32)
+    out = torch.empty(N, dtype=torch.float32, device=X.device)
+    a = 0
+    while a < N:
+        b = min(a + chunk, N)
+        if b - a < chunk:
+            a = N - chunk
+        out[a:b] = (X[a:b] * X[a:b]).sum(dim=1).to(torch.float32)
+        a = b
+    return out
+
+
+def default_mode() -> int:
+    m = os.environ.get("CORESETS_B200_MODE", "prune").strip().lower()
+    if m not in ("prune", "dense"):
+        raise ValueError(f"CORESETS_B200_MODE must be 'prune' or 'dense', got {m!r}")
+    return MODE_DENSE if m == "dense" else MODE_PRUNE
+
+
+def _graph_picks() -> int:
+    return max(1, int(os.environ.get("CORESETS_B200_GRAPH_PICKS", "32")))
+
+
+def _graphs_enabled() -> bool:
+    return bool(int(os.environ.get("CORESETS_B200_GRAPH", "1")))
+
+
+class ShardEngine:
+    """State of one rank: ``X_local`` (borrowed), norms, ``h``, ``voronoi`` (int32), the
+    replicated centre table and the control block.  ``world_size > 1`` adds the candidate packs
+    and the all-gather on ``group``."""
+
+    def __init__(self, X_local: torch.Tensor, norms: torch.Tensor, cap: int, *, shard_offset: int = 0,
+                 world_size: int = 1, group=None, mode: Optional[int] = None,
+                 h: Optional[torch.Tensor] = None, voronoi: Optional[torch.Tensor] = None,
+                 record: bool = True):
+        if X_local.dim() != 2:
+            raise ValueError(f"X_local must be 2-D, got shape {tuple(X_local.shape)}")
+        if X_local.dtype != torch.float32:
+            raise ValueError(f"the sm_100a engine computes in float32 only, got {X_local.dtype}")
+        if not X_local.is_contiguous():
+            raise ValueError("X_local must be contiguous (row-major)")
+        self.native = _native.get_native()
+        self.X = X_local
+        self.norms = norms
+        self.device = X_local.device
+        self.on_cuda = X_local.is_cuda
+        self.N_local, self.D = int(X_local.shape[0]), int(X_local.shape[1])
+        self.cap = int(cap)
+        self.shard_offset = int(shard_offset)
+        self.world_size = int(world_size)
+        self.group = group
+        self.mode = default_mode() if mode is None else int(mode)
+        dev = self.device
+        f32, i32, i64 = torch.float32, torch.int32, torch.int64
+        n_alloc = max(self.N_local, 1)
+        self.h = h if h is not None else torch.empty(n_alloc, dtype=f32, device=dev)
+        self.voronoi = voronoi if voronoi is not None else torch.empty(n_alloc, dtype=i32, device=dev)
+        self.X_sel = torch.empty((self.cap, self.D), dtype=f32, device=dev)
+        self.norms_sel = torch.empty(self.cap, dtype=f32, device=dev)
+        self.dSL = torch.empty(self.cap, dtype=f32, device=dev)
+        self.selected = torch.empty(self.cap, dtype=i64, device=dev) if record else None
+        self.eps = torch.empty(self.cap, dtype=f32, device=dev) if record else None
+        self.ctl = torch.zeros(_native.CS_CTL_BYTES // 8, dtype=i64, device=dev)
+        if self.world_size > 1:
+            self.pack_local = torch.zeros(4 + self.D, dtype=i32, device=dev)
+            self.pack_all = torch.zeros((self.world_size, 4 + self.D), dtype=i32, device=dev)
+        else:
+            self.pack_local = None
+            self.pack_all = None
+        self._ctl_host = torch.empty(_native.CS_CTL_BYTES // 8, dtype=i64,
+                                     pin_memory=self.on_cuda)
+        self._graphs = {}
+        self.state = self._make_state()
+
+    # -- plumbing ------------------------------------------------------------------------------
+    def _make_state(self) -> CsState:
+        s = CsState()
+        s.X = self.X.data_ptr() if self.N_local > 0 else None
+        s.norms = self.norms.data_ptr() if self.N_local > 0 else None
+        s.h = self.h.data_ptr()
+        s.voronoi = self.voronoi.data_ptr()
+        s.N_local = self.N_local
+        s.shard_offset = self.shard_offset
+        s.D = self.D
+        s.world_size = self.world_size
+        s.X_sel = self.X_sel.data_ptr()
+        s.norms_sel = self.norms_sel.data_ptr()
+        s.dSL_quarter = self.dSL.data_ptr()
+        s.cap = self.cap
+        s.selected = self.selected.data_ptr() if self.selected is not None else None
+        s.eps = self.eps.data_ptr() if self.eps is not None else None
+        s.ctl = self.ctl.data_ptr()
+        s.pack_local = self.pack_local.data_ptr() if self.pack_local is not None else None
+        s.pack_all = self.pack_all.data_ptr() if self.pack_all is not None else None
+        return s
+
+    def rebind(self, *, h: Optional[torch.Tensor] = None, voronoi: Optional[torch.Tensor] = None) -> None:
+        """Point the engine at other ``h`` / ``voronoi`` buffers (snapshots, probe scratch).
+        Captured graphs hold the old pointers, so they are dropped."""
+        if h is not None:
+            self.h = h
+        if voronoi is not None:
+            self.voronoi = voronoi
+        self.state = self._make_state()
+        self._graphs.clear()
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream if self.on_cuda else 0
+
+    # -- single launches -------------------------------------------------------------------------
+    def init_state(self) -> None:
+        self.native.init_state(self.state, self._stream())
+
+    def reset_ctl(self, n_sel: int) -> None:
+        self.native.reset_ctl(self.state, int(n_sel), self._stream())
+
+    def force_pick(self, global_idx: int, val: float = float("inf")) -> None:
+        self.native.force_pick(self.state, int(global_idx), float(val), self._stream())
+
+    def exchange(self) -> None:
+        if self.world_size > 1:
+            dist.all_gather_into_tensor(self.pack_all.view(-1), self.pack_local, group=self.group)
+
+    def commit(self, rules: int = RULE_NONE) -> None:
+        self.native.commit_bound(self.state, int(rules), self._stream())
+
+    def step(self, mode: Optional[int] = None) -> None:
+        self.native.fps_step(self.state, self.mode if mode is None else int(mode), self._stream())
+
+    # -- picks -------------------------------------------------------------------------------------
+    def _pick_body(self, rules: int) -> None:
+        self.exchange()
+        self.commit(rules)
+        self.step()
+
+    def pick_forced(self, global_idx: int, val: float = float("inf"), rules: int = RULE_NONE) -> None:
+        """Commit a prescribed row as the next centre and run its update."""
+        self.force_pick(global_idx, val)
+        self._pick_body(rules)
+
+    def _graph(self, n: int, rules: int):
+        key = (n, rules, self.mode)
+        g = self._graphs.get(key)
+        if g is None:
+            g = torch.cuda.CUDAGraph()
+            # side-stream warm-up is not needed: every kernel has run eagerly (the first pick)
+            with torch.cuda.graph(g):
+                for _ in range(n):
+                    self._pick_body(rules)
+            self._graphs[key] = g
+        return g
+
+    def run_picks(self, n: int, rules: int = RULE_NONE) -> None:
+        """Enqueue ``n`` farthest-point picks.  No host synchronisation happens here."""
+        n = int(n)
+        if n <= 0:
+            return
+        if self.on_cuda and _graphs_enabled():
+            unit = _graph_picks()
+            while n >= unit:
+                self._graph(unit, rules).replay()
+                n -= unit
+        for _ in range(n):
+            self._pick_body(rules)
+
+    # -- read-back -----------------------------------------------------------------------------------
+    def read_ctl(self) -> CtlView:
+        """Copy the control block to the host (synchronises the current stream)."""
+        if self.on_cuda:
+            self._ctl_host.copy_(self.ctl, non_blocking=True)
+            torch.cuda.current_stream(self.device).synchronize()
+            src = self._ctl_host
+        else:
+            src = self.ctl
+        view = CtlView()
+        ctypes.memmove(ctypes.addressof(view), src.data_ptr(), _native.CS_CTL_BYTES)
+        return view
+
+    def check_status(self) -> CtlView:
+        view = self.read_ctl()
+        if view.status != 0:
+            what = {1: "more picks were launched than the centre table can hold",
+                    2: "a forced pick named a row this rank does not own"}.get(view.status, "unknown")
+            raise RuntimeError(f"coresets_b200 device status {view.status}: {what}")
+        return view

@@ -1,0 +1,181 @@
+/*
+ * coresets_b200 -- C ABI of the B200 (sm_100a) farthest-point-sampling engine.
+ *
+ * This is the boundary a host language binds (Python/ctypes in this package).  It replaces
+ * the reference's pybind11 module `coreset_kernels`
+ * (src/coresets/cuda/kernels/bindings.cu:3-152), whose functions take torch::Tensor
+ * arguments, have no return code and no stream parameter.
+ *
+ * Conventions
+ *   - every function returns 0 (CS_OK) or a negative CS_E_* code; nothing throws or traps;
+ *   - all pointers are DEVICE pointers owned by the caller unless a comment says "host";
+ *     no entry point declared before the "self-contained" section allocates or frees memory;
+ *   - work is enqueued on the given stream and is capturable into a CUDA graph (no implicit
+ *     synchronisation, no host round trip);
+ *   - rows are addressed with 64-bit arithmetic; GLOBAL row indices must stay below 2^31
+ *     (the reference rejects more, src/coresets/cuda/multi/fps_sharded.py:68-73).
+ *
+ * One FPS pick is two launches on every rank (plus one all-gather when world_size > 1):
+ *   cs_commit_bound  resolve the winner, append it as centre n_sel, mark its row selected,
+ *                    compute the triangle bounds dSL_quarter[0..n_sel)
+ *   cs_fps_step      distance of every live row to centre n_sel, in-place min-update of h and
+ *                    voronoi, fused (value, smallest global index) arg-max for the NEXT pick,
+ *                    n_sel += 1, and (world_size > 1) the rank's candidate pack
+ */
+#ifndef CORESETS_B200_H
+#define CORESETS_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CS_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define CS_API __attribute__((visibility("default")))
+#else
+#define CS_API
+#endif
+
+/* error codes */
+#define CS_OK 0
+#define CS_E_ARG (-1)      /* null pointer, negative size, bad flag */
+#define CS_E_ALIGN (-2)    /* X / X_sel / pack not 16-byte aligned while D % 4 == 0 */
+#define CS_E_RANGE (-3)    /* global index space >= 2^31, or a size above a stated maximum */
+#define CS_E_LAUNCH (-4)   /* the CUDA runtime refused the launch (see cs_last_cuda_error) */
+#define CS_E_DEVICE (-5)   /* no usable sm_100 device / wrong architecture */
+
+/* cs_fps_step flags */
+#define CS_MODE_PRUNE 0u   /* rows excluded by the triangle bound are not loaded (default) */
+#define CS_MODE_DENSE 1u   /* every live row's distance is computed; the bound only masks the
+                              update, so results are identical to CS_MODE_PRUNE */
+/* cs_commit_bound flags */
+#define CS_RULE_NONE 0u    /* plain FPS: no separation bookkeeping */
+#define CS_RULE_SIM_SINGLE 1u   /* commit_center_with_sep_kernel rules (commit.cu:41-51) */
+#define CS_RULE_SIM_SHARDED 2u  /* reduce_and_commit_multi_sharded_kernel rules (multi.cu:331-340) */
+
+/* Size in bytes of the per-run device control block (n_sel counter, the two arg-max key
+ * slots, ticket, status, separation / viability words).  Zero it with cs_reset_ctl. */
+#define CS_CTL_BYTES 256
+
+/* Host-visible mirror of the control block (read it back with one 256-byte copy). */
+typedef struct cs_ctl_view {
+    uint64_t key[2];     /* arg-max key for pick i lives in key[i & 1]                      */
+    int32_t n_sel;       /* centres committed so far                                          */
+    uint32_t ticket;     /* blocks of the running step kernel that have finished              */
+    int32_t status;      /* sticky device-side error (0 = none)                               */
+    int32_t viable;      /* simulation: 1 once separation beat coverage                       */
+    float sep;           /* simulation: running min of the pick values                        */
+    int32_t steps;       /* simulation: picks committed since cs_sim_begin                    */
+    uint64_t live_rows;  /* rows whose distance the last cs_fps_step evaluated               */
+    float last_val;      /* value (max h) of the last committed pick                          */
+    int32_t last_idx;    /* global index of the last committed pick (-1: nothing left)       */
+    uint8_t reserved[CS_CTL_BYTES - 56];
+} cs_ctl_view;
+
+/*
+ * One rank's view of a run.  Filled by the host once; the library only reads it.
+ * A candidate pack is (4 + D) 32-bit words: key low, key high, norm bits, 0, row bits[D].
+ */
+typedef struct cs_state {
+    const float* X;        /* [N_local, D] row-major fp32                                     */
+    const float* norms;    /* [N_local] squared row norms                                     */
+    float* h;              /* [N_local] squared distance to nearest centre; -1 = selected     */
+    int32_t* voronoi;      /* [N_local] slot of the nearest centre (reference: int64)         */
+    int64_t N_local;       /* rows on this rank (0 is legal)                                  */
+    int64_t shard_offset;  /* global index of local row 0                                     */
+    int32_t D;             /* row length                                                      */
+    int32_t world_size;    /* ranks taking part (1 = no exchange)                             */
+    float* X_sel;          /* [cap, D] committed centres (replicated on every rank)           */
+    float* norms_sel;      /* [cap]                                                           */
+    float* dSL_quarter;    /* [cap] triangle bounds of the pick in flight                     */
+    int64_t cap;           /* capacity of the three arrays above and of selected / eps        */
+    int64_t* selected;     /* [cap] global index per slot, or NULL                            */
+    float* eps;            /* [cap] max h before each pick, or NULL                           */
+    void* ctl;             /* CS_CTL_BYTES control block                                      */
+    uint32_t* pack_local;  /* [4 + D] this rank's candidate (world_size > 1), else NULL       */
+    const uint32_t* pack_all; /* [world_size, 4 + D] all-gathered candidates, else NULL       */
+} cs_state;
+
+typedef void* cs_stream; /* cudaStream_t */
+
+/* ABI version of the loaded library (CS_ABI_VERSION). */
+CS_API int cs_version(void);
+
+/* Static description of an error code. */
+CS_API const char* cs_error_string(int code);
+
+/* Last CUDA runtime error string seen by a failing launch on the calling thread. */
+CS_API const char* cs_last_cuda_error(void);
+
+/* Number of SMs of the current device, or a negative code.  Also verifies that the device
+ * is compute capability 10.x, which the embedded sm_100a code requires. */
+CS_API int cs_device_check(void);
+
+/*
+ * h[i] = +inf, voronoi[i] = 0 for every local row, and a zeroed control block.
+ * Replaces the torch.full / torch.zeros state set-up of src/coresets/cuda/fps.py:37-43 and
+ * src/coresets/cuda/multi/fps_sharded.py:113-119.
+ */
+CS_API int cs_init_state(const cs_state* s, cs_stream stream);
+
+/* Zero the control block only, then set n_sel (used when a run continues from a state that
+ * already holds n_sel centres, e.g. a bisect probe). */
+CS_API int cs_reset_ctl(const cs_state* s, int32_t n_sel, cs_stream stream);
+
+/*
+ * Force the next pick to be global row `global_idx` with value `val` (+inf for a seed).
+ * The owner rank publishes the candidate, every other rank publishes "nothing".  Replaces
+ * `d_out_idx.fill_(new_idx)` of cuda/_internal/voronoi_step.py:25 and `pack_row_by_owner`
+ * of cuda/multi/fps_sharded.py:131-146.  Follow with the all-gather (world_size > 1),
+ * cs_commit_bound and cs_fps_step exactly like a normal pick.
+ */
+CS_API int cs_force_pick(const cs_state* s, int64_t global_idx, float val, cs_stream stream);
+
+/*
+ * Resolve and commit pick number i = n_sel.  The winner is the largest key among the
+ * world_size candidates (value first, then smallest global index: argmax_better,
+ * kernels/_shared.cuh:24-27).  Writes selected[i], eps[i], X_sel[i], norms_sel[i]; the
+ * owner sets h = -1 and voronoi = i on the row; then dSL_quarter[v] for every v < i.
+ * `rules` selects the separation / viability bookkeeping of the simulation loops.
+ * Replaces commit_center_cuda, commit_center_with_sep_cuda, compute_dSL_quarter_cuda
+ * (kernels/commit.cu:162-210), reduce_and_commit_multi_sharded_cuda (kernels/multi.cu:407-422)
+ * and the host-side torch.argmax + .item() of cuda/multi/fps_sharded.py:173-176.
+ */
+CS_API int cs_commit_bound(const cs_state* s, uint32_t rules, cs_stream stream);
+
+/*
+ * The fused hot kernel.  For centre i = n_sel (slot written by cs_commit_bound):
+ *   rows with h < 0 are skipped; for i > 0 rows with dSL_quarter[voronoi] >= h are not
+ *   updated; d = norms[row] + norm_new - 2*dot(row, centre) with the reference's summation
+ *   order; if d < h then h = d, voronoi = i; every row then feeds (h, global index) into a
+ *   block -> grid arg-max whose result is the key of pick i + 1; n_sel becomes i + 1.
+ * Replaces fps_update_cuda, voronoi_update_cuda (kernels/warp.cu:159-191), argmax_cuda
+ * (kernels/argmax.cu:179-193) and pack_argmax_with_row_cuda / fill_pack_with_row_neg_inf_cuda
+ * (kernels/multi.cu:387-405).
+ */
+CS_API int cs_fps_step(const cs_state* s, uint32_t mode, cs_stream stream);
+
+/* Start a simulation (bisect probe): zero viable / steps, set the running separation.
+ * Replaces the two blocking cudaMemcpy of kernels/simulate.cu:27-29, multi.cu:448-451. */
+CS_API int cs_sim_begin(const cs_state* s, float sep, cs_stream stream);
+
+/* Tail check of a simulation: viable |= sep > (max h after the last update); the max is the
+ * best candidate value over all ranks.  Replaces final_viable_check_kernel
+ * (kernels/argmax.cu:152-159) and final_viable_check_multi_sharded_kernel (multi.cu:369-384). */
+CS_API int cs_sim_final_check(const cs_state* s, cs_stream stream);
+
+/*
+ * Several probes at once: `n_lanes` (1..8) independent states that share X / norms /
+ * N_local / D / shard_offset / world_size but own their h, voronoi, centres and control
+ * block.  One pass over X serves every lane; each lane's arithmetic is that of cs_fps_step.
+ * Replaces voronoi_update_lanes_kernel (kernels/multi.cu:569-708).
+ */
+CS_API int cs_fps_step_lanes(const cs_state* lanes, int32_t n_lanes, uint32_t mode, cs_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CORESETS_B200_H */

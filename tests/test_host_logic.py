@@ -1,0 +1,66 @@
+"""Host-side drivers on CPU: the pick sequencing of fps_cuda / fps_sharded is driven with the
+oracle-backed stand-in native library and compared with the oracle's own whole-run functions."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from coresets_b200 import _native
+import importlib
+
+fps_mod = importlib.import_module("coresets_b200.cuda.fps")
+from tests.data import clustered_jitter, gaussian_mixture, with_duplicates
+from tests.fake_native import FakeNative
+
+
+@pytest.fixture()
+def fake_native(monkeypatch):
+    monkeypatch.setattr(_native, "_native", FakeNative())
+    monkeypatch.setattr(fps_mod, "_REQUIRE_CUDA", False)
+    yield
+
+
+def _norms_t(X):
+    return (X * X).sum(dim=1).to(torch.float32).numpy()
+
+
+@pytest.mark.parametrize("N,D,k", [(1, 4, 1), (33, 8, 33), (500, 32, 64), (777, 6, 50), (2048, 64, 128)])
+def test_fps_cuda_driver_matches_oracle(fake_native, N, D, k):
+    X = torch.from_numpy(gaussian_mixture(N, D, 8, seed=N))
+    sel, eps = fps_mod.fps(X, k, return_epsilons=True)
+    o_sel, o_eps, _, _ = oracle.fps_cuda(X.numpy(), _norms_t(X), k)
+    assert sel.dtype == torch.int64
+    np.testing.assert_array_equal(sel.numpy(), o_sel)
+    np.testing.assert_array_equal(eps.numpy().view(np.int32), o_eps.view(np.int32))
+
+
+def test_fps_cuda_seed_tensor(fake_native):
+    X = torch.from_numpy(with_duplicates(clustered_jitter(600, 16), 40, seed=1))
+    seed = torch.tensor([5, 17, 301])
+    sel = fps_mod.fps(X, 40, seed=seed)
+    o_sel, _, _, _ = oracle.fps_cuda(X.numpy(), _norms_t(X), 40, seed=seed.numpy())
+    np.testing.assert_array_equal(sel.numpy(), o_sel)
+    assert sel[:3].tolist() == [5, 17, 301]
+
+
+def test_fps_cuda_validation(fake_native):
+    X = torch.zeros(10, 4)
+    with pytest.raises(ValueError):
+        fps_mod.fps(torch.zeros(10), 2)
+    with pytest.raises(ValueError):
+        fps_mod.fps(X, 0)
+    with pytest.raises(ValueError):
+        fps_mod.fps(X, 11)
+    with pytest.raises(ValueError):
+        fps_mod.fps(X, 2, seed=torch.zeros((2, 2), dtype=torch.long))
+    with pytest.raises(ValueError):
+        fps_mod.fps(X, 2, seed=torch.tensor([1, 2, 3]))
+    with pytest.raises(ValueError):
+        fps_mod.fps(X, 2, seed=torch.tensor([], dtype=torch.long))
+    with pytest.raises(ValueError):
+        fps_mod.fps(X.double(), 2)
+
+
+def test_fps_cuda_requires_cuda_tensor():
+    with pytest.raises(ValueError, match="CUDA"):
+        fps_mod.fps(torch.zeros(10, 4), 2)
