@@ -1,0 +1,387 @@
+"""Benchmark of the farthest-point-sampling hot path.
+
+    python bench.py --gpus 1 --steps K --warmup W            (one process)
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...                       (the reference's CPU `fps`)
+
+A "step" is ONE FPS pick over the resident matrix: the bound kernel plus the fused
+distance / min-update / arg-max kernel on every rank, plus the candidate all-gather when N > 1.
+The headline line is measured in DENSE mode (every live row's distance is evaluated each pick --
+the bandwidth-bound pass the roofline is about, and what the reference's CPU `fps` does); the
+`prune` object reports the default product mode (triangle-bound skip, identical picks).
+
+Workload: the 300M x 128 fp32 mixture ("c3"), rows split over the ranks with
+compute_shard_layout (strong scaling).  Inputs are synthetic, generated on the device from
+(seed, row block).  X is far larger than the 126 MB L2, so no flush is needed between steps.
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+METRIC = "fps_picks_per_s"
+UNIT = "picks/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=24)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3")
+    ap.add_argument("--rows", type=int, default=0, help="override the workload's global row count")
+    ap.add_argument("--prune-picks", type=int, default=384, help="picks run before the prune-mode timing")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-prune", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-rows", type=int, default=2_000_000)
+    return ap.parse_args()
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons for one GPU while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.rows = []
+        self.proc = None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device).uuid)
+            ident = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={ident}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._pump, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=3)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, val in zip(names, f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_max(x: float, device) -> float:
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    return x
+
+
+def barrier_sync(device):
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+
+
+# ------------------------------------------------------------------------------------- CPU arms
+def cpu_reference_fn():
+    """The reference's own CPU `fps` when its package travelled with the repo (oracle/_ref/site),
+    else the port in oracle/cpu_fps.py."""
+    site = ROOT / "oracle" / "_ref" / "site"
+    if (site / "coresets" / "pytorch" / "fps.py").is_file():
+        sys.path.insert(0, str(site))
+        try:
+            from coresets.pytorch.fps import fps as ref_fps
+            return ref_fps, "reference"
+        except Exception:
+            pass
+    from oracle.cpu_fps import fps as port_fps
+    return port_fps, "port"
+
+
+def cpu_arm(w, rows: int, steps: int, warmup: int) -> dict:
+    from coresets_b200.synth import MixtureSource, scaled
+    fn, kind = cpu_reference_fn()
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    rows = min(rows, w.n_rows)
+    ws = scaled(w, rows)
+    X = MixtureSource(ws).rows(0, rows, torch.device("cpu"))
+    fn(X, max(warmup, 2))                       # TorchScript / BLAS warm-up, untimed
+    t0 = time.perf_counter()
+    fn(X, steps)
+    dt = time.perf_counter() - t0
+    sample_rate = steps / dt
+    full_rate = sample_rate * rows / w.n_rows   # a dense pick is linear in the row count
+    return {"value": full_rate, "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": f"{steps} dense picks on the first {rows} rows of {w.name} ({w.dim} cols) in {dt:.2f} s = "
+                      f"{sample_rate:.2f} picks/s on the sample, scaled by {rows}/{w.n_rows} rows",
+            "sample_picks_per_s": sample_rate, "ms_per_step_sample": 1e3 * dt / steps}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from coresets_b200.synth import WORKLOADS, scaled
+    w = WORKLOADS[args.workload]
+    if args.rows:
+        w = scaled(w, args.rows, k=w.k)
+    steps = max(args.steps, 1)
+    cb = cpu_arm(w, args.cpu_rows, steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": 1e3 / cb["value"], "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{w.name}: {w.describe}", "rows": w.n_rows, "dim": w.dim, "mode": "dense (reference CPU fps)"},
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    from coresets_b200 import _native, engine
+    from coresets_b200._native import MODE_DENSE, MODE_PRUNE
+    from coresets_b200.cuda.multi.layout import compute_shard_layout
+    from coresets_b200.synth import WORKLOADS, MixtureSource, scaled
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    native = _native.get_native()
+    sms = native.device_check()
+
+    w = WORKLOADS[args.workload]
+    if args.rows:
+        w = scaled(w, args.rows, k=w.k)
+    sizes, offsets = compute_shard_layout(w.n_rows, world)
+    n_local, off = sizes[rank], offsets[rank]
+    K, W = max(args.steps, 1), max(args.warmup, 0)
+    k_kernel = min(K, 12)
+    do_prune = not args.no_prune
+    cap = 1 + W + K + k_kernel + ((args.prune_picks + K + 4) if do_prune else 0) + 8
+
+    need = n_local * (w.dim * 4 + 12) + (2 << 30)
+    free_b, total_b = torch.cuda.mem_get_info(device)
+    if need > free_b:
+        raise SystemExit(f"rank {rank}: needs {need/1e9:.1f} GB of device memory, {free_b/1e9:.1f} GB free")
+
+    t_gen = time.time()
+    src = MixtureSource(w)
+    X = torch.empty((n_local, w.dim), dtype=torch.float32, device=device)
+    src.fill(X, off)
+    norms = engine.row_norms(X)
+    torch.cuda.synchronize(device)
+    t_gen = time.time() - t_gen
+
+    eng = engine.ShardEngine(X, norms, cap, shard_offset=off, world_size=world, mode=MODE_DENSE)
+    eng.init_state()
+    eng.pick_forced(0)
+    eng.prepare(max(W, 1))
+    eng.prepare(K)
+    eng.run_picks(W)
+    barrier_sync(device)
+
+    # ---- timed region: K picks, inputs resident in HBM --------------------------------------
+    sampler = ClockSampler(local) if rank == 0 else None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier_sync(device)
+    ev0.record()
+    eng.run_picks(K)
+    ev1.record()
+    barrier_sync(device)
+    ms_total = dist_max(ev0.elapsed_time(ev1), device)
+    clocks = sampler.stop() if sampler else None
+    eng.check_status()
+    value = K / (ms_total / 1e3)
+
+    # ---- per-kernel timing of the fused step kernel (roofline) and of the exchange ----------
+    ea = [torch.cuda.Event(enable_timing=True) for _ in range(3 * k_kernel)]
+    for j in range(k_kernel):
+        ea[3 * j].record()
+        eng.exchange()
+        ea[3 * j + 1].record()
+        eng.commit()
+        ea[3 * j + 2].record()
+        eng.step()
+    tail = torch.cuda.Event(enable_timing=True)
+    tail.record()
+    torch.cuda.synchronize(device)
+    step_ms, xchg_ms, commit_ms = [], [], []
+    for j in range(k_kernel):
+        nxt = ea[3 * j + 3] if j + 1 < k_kernel else tail
+        xchg_ms.append(ea[3 * j].elapsed_time(ea[3 * j + 1]))
+        commit_ms.append(ea[3 * j + 1].elapsed_time(ea[3 * j + 2]))
+        step_ms.append(ea[3 * j + 2].elapsed_time(nxt))
+    kern_ms = dist_max(statistics.mean(step_ms), device)
+    algo_bytes = max(sizes) * (4 * w.dim + 8)                # per launch, the largest shard
+    achieved = algo_bytes / (kern_ms / 1e3) / 1e9
+    peak, peak_kind = peaks()
+    live_dense = eng.read_ctl().live_rows
+
+    # ---- default product mode (triangle-bound skip) -------------------------------------------
+    prune = None
+    if do_prune:
+        eng.mode = MODE_PRUNE
+        eng.prepare(K)
+        eng.run_picks(args.prune_picks)
+        barrier_sync(device)
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        eng.run_picks(K)
+        p1.record()
+        barrier_sync(device)
+        p_ms = dist_max(p0.elapsed_time(p1), device)
+        ctl = eng.check_status()
+        prune = {"value": K / (p_ms / 1e3), "unit": UNIT, "ms_per_step": p_ms / K,
+                 "picks_before": 1 + W + K + k_kernel + args.prune_picks,
+                 "live_rows_last_step_rank0": int(ctl.live_rows), "rows_rank0": n_local}
+
+    # ---- end to end through the public API: host X -> device -> picks -> host -----------------
+    e2e = None
+    if not args.no_e2e:
+        del eng, norms
+        torch.cuda.empty_cache()
+        e2e = run_e2e(args, X, w, world, rank, device, K, W, off)
+
+    cpu_b = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_b = cpu_arm(w, args.cpu_rows, 24, 3)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{w.name}: {w.describe}", "rows": w.n_rows, "dim": w.dim,
+                       "rows_per_gpu": max(sizes), "mode": "dense", "first_pick": 0,
+                       "l2": "inputs (>= 19 GB per GPU) exceed the 126 MB L2; no flush",
+                       "exchange": "one NCCL all-gather of (4+D) words per rank per pick" if world > 1 else "none",
+                       "generate_s": round(t_gen, 2), "sms": sms},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": peak_kind, "traffic": None, "kernel": "fps_step_kernel (dense)",
+                         "kernel_ms": kern_ms, "algorithmic_bytes_per_launch": algo_bytes,
+                         "live_rows_last_launch_rank0": int(live_dense)},
+            "step_breakdown_ms": {"fps_step": kern_ms, "commit_bound": statistics.mean(commit_ms),
+                                  "exchange": statistics.mean(xchg_ms) if world > 1 else 0.0},
+            "prune": prune, "e2e": e2e, "cpu_baseline": cpu_b, "clocks": clocks,
+            "gpu_launches": 2 * K,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_e2e(args, X, w, world, rank, device, K, W, off):
+    """One complete job through the public API shape: pinned host X -> H2D -> norms -> first pick ->
+    K picks -> D2H of (selected, epsilons).  The W warm-up picks between the load phase and the K
+    timed picks are not counted.  Returns None (with the reason) when the host cannot pin X."""
+    from coresets_b200 import engine
+    from coresets_b200._native import MODE_DENSE
+    import psutil
+    n_local, dim = X.shape
+    nbytes = n_local * dim * 4
+    avail = psutil.virtual_memory().available
+    ok = torch.tensor([1 if nbytes * 1.10 + (8 << 30) < avail / max(1, min(world, torch.cuda.device_count())) else 0],
+                      device=device)
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if int(ok.item()) == 0:
+        return {"value": None, "unit": UNIT, "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
+                "skipped": f"host cannot pin {nbytes/1e9:.1f} GB per rank ({avail/1e9:.1f} GB available)"}
+    host = torch.empty((n_local, dim), dtype=torch.float32, pin_memory=True)
+    host.copy_(X)
+    torch.cuda.synchronize(device)
+    sel_host = torch.empty(1 + W + K, dtype=torch.int64, pin_memory=True)
+    eps_host = torch.empty(1 + W + K, dtype=torch.float32, pin_memory=True)
+    X.zero_()
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    barrier_sync(device)
+    e[0].record()
+    X.copy_(host, non_blocking=True)
+    norms = engine.row_norms(X)
+    eng2 = engine.ShardEngine(X, norms, 1 + W + K, shard_offset=off, world_size=world, mode=MODE_DENSE)
+    eng2.init_state()
+    eng2.pick_forced(0)
+    e[1].record()
+    eng2.prepare(K)
+    eng2.run_picks(W)
+    barrier_sync(device)
+    e[2].record()
+    eng2.run_picks(K)
+    sel_host.copy_(eng2.selected, non_blocking=True)
+    eps_host.copy_(eng2.eps, non_blocking=True)
+    e[3].record()
+    barrier_sync(device)
+    load_ms = dist_max(e[0].elapsed_time(e[1]), device)
+    picks_ms = dist_max(e[2].elapsed_time(e[3]), device)
+    eng2.check_status()
+    total_s = (load_ms + picks_ms) / 1e3
+    return {"value": K / total_s, "unit": UNIT, "h2d_bytes_per_step": nbytes * world / K,
+            "d2h_bytes_per_step": 12.0 * (1 + W + K) / K, "load_ms": load_ms, "picks_ms": picks_ms,
+            "what": f"one job of {K} picks: pinned-host X -> device ({nbytes/1e9:.1f} GB per rank), norms, first "
+                    f"pick, {K} picks, read-back of selected/epsilons; H2D amortised over the {K} picks"}
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

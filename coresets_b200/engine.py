@@ -184,16 +184,32 @@ class ShardEngine:
             self._graphs[key] = g
         return g
 
+    _UNITS = (32, 16, 8, 4, 2, 1)
+
+    def prepare(self, n: int, rules: int = RULE_NONE) -> None:
+        """Capture (without running) the graphs ``run_picks(n)`` will replay."""
+        if not (self.on_cuda and _graphs_enabled()):
+            return
+        top = min(_graph_picks(), self._UNITS[0])
+        for unit in self._UNITS:
+            if unit <= top and n >= unit:
+                self._graph(unit, rules)
+                n %= unit
+
     def run_picks(self, n: int, rules: int = RULE_NONE) -> None:
-        """Enqueue ``n`` farthest-point picks.  No host synchronisation happens here."""
+        """Enqueue ``n`` farthest-point picks.  No host synchronisation happens here: the picks
+        are replayed from CUDA graphs of 32, 16, ... 1 picks (binary decomposition of ``n``)."""
         n = int(n)
         if n <= 0:
             return
         if self.on_cuda and _graphs_enabled():
-            unit = _graph_picks()
-            while n >= unit:
-                self._graph(unit, rules).replay()
-                n -= unit
+            top = min(_graph_picks(), self._UNITS[0])
+            for unit in self._UNITS:
+                if unit > top:
+                    continue
+                while n >= unit:
+                    self._graph(unit, rules).replay()
+                    n -= unit
         for _ in range(n):
             self._pick_body(rules)
 

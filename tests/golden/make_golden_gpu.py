@@ -1,0 +1,193 @@
+"""Generate the golden vectors under tests/golden/ by running the REFERENCE's own CUDA path on a GPU.
+
+Needs (all git-ignored, produced on a machine that has the reference checkout):
+  oracle/_ref/site/   `pip install --no-deps --target oracle/_ref/site <reference checkout>`
+  oracle/_ref/build/  `python oracle/build_ref.py` (the reference's kernels, its own flags)
+
+Run on a B200:   python tests/golden/make_golden_gpu.py --out gpurun_out/golden
+then copy the produced *.npz next to this file.  Each file holds the inputs that cannot be
+regenerated bit-exactly elsewhere (the float32 row norms torch computed on the GPU) and the
+reference's outputs: `selected` from its public `fps_cuda`, `selected`/`epsilons` from its
+`fps_sharded` (one-rank NCCL group), and `h` / `voronoi` / `eps` from a transparent re-run of
+its driver loop (`voronoi_step` + `argmax_cuda`, src/coresets/cuda/fps.py:105-128) that must
+reproduce `fps_cuda`'s picks.  X itself is regenerated from tests/data.py (numpy, seeded).
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.machinery
+import importlib.util
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "oracle" / "_ref" / "site"))
+
+from tests import data as tdata  # noqa: E402
+
+CASES = [
+    # name, generator, kwargs, K, seeds
+    ("ref_script_8192x32", "clustered_jitter", dict(N=8192, D=32, seed=42), 2048, None),
+    ("mix_4097x128", "gaussian_mixture", dict(N=4097, D=128, n_comp=8, seed=4225), 300, None),
+    ("mix_2500x256", "gaussian_mixture", dict(N=2500, D=256, n_comp=8, seed=2756), 200, None),
+    ("mix_900x1024", "gaussian_mixture", dict(N=900, D=1024, n_comp=8, seed=1924), 48, None),
+    ("mix_33x64", "gaussian_mixture", dict(N=33, D=64, n_comp=8, seed=97), 20, None),
+    ("mix_800x50", "gaussian_mixture", dict(N=800, D=50, n_comp=8, seed=850), 64, None),
+    ("uneven_16383x128", "gaussian_mixture", dict(N=16383, D=128, n_comp=8, seed=16511), 512, None),
+    ("c1_20000x64", "gaussian_mixture", dict(N=20000, D=64, n_comp=16, seed=0), 512, None),
+    ("dups_3000x16", "dups", dict(N=3000, D=16, seed=5), 1500, None),
+    ("seeded_5000x64", "gaussian_mixture", dict(N=5000, D=64, n_comp=8, seed=3), 200, [17, 4000, 123]),
+]
+
+
+def make_x(gen: str, kw: dict) -> np.ndarray:
+    if gen == "dups":
+        return tdata.with_duplicates(tdata.clustered_jitter(kw["N"], kw["D"], seed=kw["seed"]), 600, seed=9)
+    return getattr(tdata, gen)(**kw)
+
+
+def load_reference():
+    so = ROOT / "oracle" / "_ref" / "build" / "coreset_kernels.so"
+    loader = importlib.machinery.ExtensionFileLoader("coreset_kernels", str(so))
+    spec = importlib.util.spec_from_loader("coreset_kernels", loader)
+    mod = importlib.util.module_from_spec(spec)
+    loader.exec_module(mod)
+    import coresets.cuda.extension as ext
+    ext._extension = mod
+    ext._compiled = True
+    import coresets
+    return coresets, mod
+
+
+def transparent_run(coresets, ext, X, K, seeds):
+    """The reference's fps() loop with its state kept (src/coresets/cuda/fps.py:34-128)."""
+    from coresets.cuda._internal import voronoi_step
+    dev = X.device
+    N, D = X.shape
+    norms = (X * X).sum(dim=1).to(torch.float32)
+    h = torch.full((N,), float("inf"), dtype=torch.float32, device=dev)
+    v = torch.zeros(N, dtype=torch.int64, device=dev)
+    X_sel = torch.empty((K, D), dtype=X.dtype, device=dev)
+    norms_sel = torch.empty(K, dtype=torch.float32, device=dev)
+    dSL = torch.empty(K, dtype=torch.float32, device=dev)
+    d_idx = torch.empty(1, dtype=torch.int32, device=dev)
+    d_val = torch.empty(1, dtype=torch.float32, device=dev)
+    nb = int(ext.MAX_ARGMAX_BLOCKS)
+    bv = torch.empty(nb, dtype=torch.float32, device=dev)
+    bi = torch.empty(nb, dtype=torch.int32, device=dev)
+    sel = np.empty(K, dtype=np.int64)
+    eps = np.full(K, np.inf, dtype=np.float32)
+    seeds = [0] if seeds is None else list(seeds)
+    for i, s in enumerate(seeds):
+        sel[i] = s
+        voronoi_step(X, norms, h, v, X_sel, norms_sel, dSL, d_idx, int(s), i)
+    for i in range(len(seeds), K):
+        ext.argmax_cuda(h, bv, bi, d_val, d_idx, N)
+        idx = int(d_idx.item())
+        sel[i] = idx
+        eps[i] = float(d_val.item())
+        voronoi_step(X, norms, h, v, X_sel, norms_sel, dSL, d_idx, idx, i)
+    return sel, eps, norms.cpu().numpy(), h.cpu().numpy(), v.cpu().numpy().astype(np.int32)
+
+
+def compare_with_engine(name, X, K, seeds, sel_ref, eps_ref, h_ref, v_ref):
+    """Side-by-side run of this repository's engine on the same device tensor (diagnostic)."""
+    from coresets_b200 import engine
+    norms = engine.row_norms(X)
+    eng = engine.ShardEngine(X.contiguous(), norms, K)
+    eng.init_state()
+    for s_ in ([0] if seeds is None else seeds):
+        eng.pick_forced(int(s_))
+    eng.run_picks(K - (1 if seeds is None else len(seeds)))
+    eng.check_status()
+    N = X.shape[0]
+    ok_sel = np.array_equal(eng.selected.cpu().numpy(), sel_ref)
+    ok_h = np.array_equal(eng.h[:N].cpu().numpy().view(np.int32), h_ref.view(np.int32))
+    ok_v = np.array_equal(eng.voronoi[:N].cpu().numpy(), v_ref)
+    ok_e = np.array_equal(eng.eps.cpu().numpy().view(np.int32), eps_ref.view(np.int32))
+    print(f"[compare] {name}: selected={ok_sel} h_bits={ok_h} voronoi={ok_v} eps_bits={ok_e}", flush=True)
+
+
+def midsize_compare(coresets, dev, out):
+    """Reference vs engine on larger device-generated matrices: identical picks, wall time of both."""
+    import json
+    import time
+    from coresets_b200 import engine
+    from coresets_b200.synth import WORKLOADS, MixtureSource, scaled
+    results = []
+    for wname, n_rows, K in (("c3", 2_000_000, 2000), ("c2", 5_000_000, 1000), ("c4", 400_000, 500),
+                             ("c3", 37_500_000, 1024)):
+        w = scaled(WORKLOADS[wname], n_rows, k=K)
+        X = MixtureSource(w).rows(0, n_rows, dev)
+        torch.cuda.synchronize()
+        t0 = time.time()
+        ref_sel = coresets.fps_cuda(X, K)
+        torch.cuda.synchronize()
+        t_ref = time.time() - t0
+        t0 = time.time()
+        norms = engine.row_norms(X)
+        eng = engine.ShardEngine(X, norms, K)
+        eng.init_state()
+        eng.pick_forced(0)
+        eng.run_picks(K - 1)
+        eng.check_status()
+        torch.cuda.synchronize()
+        t_new = time.time() - t0
+        same = bool(torch.equal(ref_sel, eng.selected))
+        ndiff = int((ref_sel != eng.selected).sum().item())
+        rec = dict(workload=wname, n_rows=n_rows, dim=w.dim, K=K, identical=same, n_diff=ndiff,
+                   reference_fps_cuda_s=t_ref, engine_s=t_new,
+                   reference_picks_per_s=K / t_ref, engine_picks_per_s=K / t_new)
+        print("[midsize]", json.dumps(rec), flush=True)
+        results.append(rec)
+        np.save(out / f"midsize_{wname}_{n_rows}_selected.npy", ref_sel.cpu().numpy())
+        del X, norms, eng
+        torch.cuda.empty_cache()
+    (out / "midsize_compare.json").write_text(json.dumps(results, indent=1))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", default=str(ROOT / "gpurun_out" / "golden"))
+    ap.add_argument("--compare", action="store_true", help="also run this repository's engine side by side")
+    a = ap.parse_args()
+    out = Path(a.out)
+    out.mkdir(parents=True, exist_ok=True)
+    coresets, ext = load_reference()
+    import torch.distributed as dist
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    torch.cuda.set_device(0)
+    dist.init_process_group("nccl", rank=0, world_size=1)
+    dev = torch.device("cuda:0")
+    for name, gen, kw, K, seeds in CASES:
+        X_np = make_x(gen, kw)
+        X = torch.from_numpy(X_np).to(dev)
+        seed_t = None if seeds is None else torch.tensor(seeds, dtype=torch.long)
+        sel_api = coresets.fps_cuda(X, K, seed=seed_t).cpu().numpy().astype(np.int64)
+        sel, eps, norms, h, v = transparent_run(coresets, ext, X, K, seeds)
+        assert np.array_equal(sel, sel_api), f"{name}: transparent loop diverged from fps_cuda"
+        rec = dict(generator=gen, K=K, selected=sel_api, eps=eps, norms=norms, h=h, voronoi=v,
+                   seeds=np.asarray(seeds if seeds is not None else [0], dtype=np.int64),
+                   **{f"gen_{k}": v_ for k, v_ in kw.items()})
+        if seeds is None or len(seeds) == 1:
+            s_sel, s_eps = coresets.fps_sharded(X, K, seed=None if seeds is None else int(seeds[0]), verbose=False)
+            rec["sharded_selected"] = s_sel.cpu().numpy().astype(np.int64)
+            rec["sharded_eps"] = s_eps.numpy().astype(np.float32)
+            assert np.array_equal(rec["sharded_selected"], sel_api), f"{name}: fps_sharded != fps_cuda"
+        np.savez_compressed(out / f"{name}.npz", **rec)
+        print(f"[golden] {name}: K={K} first={sel_api[:5].tolist()} last={sel_api[-3:].tolist()}", flush=True)
+        if a.compare:
+            compare_with_engine(name, X, K, seeds, sel_api, eps, h, v)
+    if a.compare:
+        midsize_compare(coresets, dev, out)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,255 @@
+"""Parity of the sm_100a kernels with the oracle, through the C ABI (ctypes -> libcoresets_b200.so).
+
+Bar: bit-exact.  `selected` identical; `h`, `epsilons` compared as raw 32-bit patterns; `voronoi`
+equal.  Norms are an input of both sides (the reference takes them from torch), so both get the
+same float32 vector computed by torch on the GPU.
+"""
+import importlib
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from coresets_b200 import _native, engine
+from coresets_b200._native import MODE_DENSE, MODE_PRUNE
+from tests.data import clustered_jitter, gaussian_mixture, with_duplicates
+
+pytestmark = pytest.mark.gpu
+fps_mod = importlib.import_module("coresets_b200.cuda.fps")
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.int32)
+
+
+def run_engine(X_np, k, *, mode=MODE_PRUNE, seed=(0,), graph=True, monkeypatch=None):
+    dev = torch.device("cuda:0")
+    X = torch.from_numpy(X_np).to(dev)
+    norms = engine.row_norms(X)
+    if monkeypatch is not None:
+        monkeypatch.setenv("CORESETS_B200_GRAPH", "1" if graph else "0")
+    eng = engine.ShardEngine(X, norms, k, mode=mode)
+    eng.init_state()
+    for s in seed:
+        eng.pick_forced(int(s))
+    eng.run_picks(k - len(seed))
+    ctl = eng.check_status()
+    assert ctl.n_sel == k
+    return eng, norms.cpu().numpy()
+
+
+def assert_matches_oracle(eng, X_np, norms_np, k, seed=(0,)):
+    o_sel, o_eps, o_h, o_v = oracle.fps_cuda(X_np, norms_np, k, seed=np.asarray(seed, dtype=np.int64))
+    N = X_np.shape[0]
+    np.testing.assert_array_equal(eng.selected.cpu().numpy(), o_sel)
+    np.testing.assert_array_equal(bits(eng.eps.cpu().numpy()), bits(o_eps))
+    np.testing.assert_array_equal(bits(eng.h[:N].cpu().numpy()), bits(o_h))
+    np.testing.assert_array_equal(eng.voronoi[:N].cpu().numpy().astype(np.int64), o_v)
+
+
+SHAPES = [
+    # N, D, k          what it exercises
+    (1, 4, 1),          # a single row
+    (31, 8, 31),        # less than one 32-row tile, every row selected
+    (33, 64, 20),       # tile + 1 ragged row; D = 64 leaves lanes 16..31 without a chunk
+    (1000, 32, 128),
+    (4097, 128, 300),   # one chunk per lane, exact
+    (3000, 192, 64),    # 1.5 chunks per lane (guarded second chunk)
+    (2500, 256, 200),   # two chunks per lane
+    (1500, 512, 64),
+    (900, 1024, 48),    # eight chunks per lane
+    (700, 1028, 40),    # D % 4 == 0 but wider than the register path: generic kernel
+    (1200, 100, 64),    # D % 4 == 0, 25 chunks
+    (800, 50, 64),      # D % 4 != 0: the reference's scalar dot
+    (600, 3, 40),
+    (16383, 128, 512),  # the reference's uneven-shard determinism config (N = 16383, D = 128)
+]
+
+
+@pytest.mark.parametrize("N,D,k", SHAPES)
+def test_fps_matches_oracle_prune(N, D, k):
+    X = gaussian_mixture(N, D, 8, seed=N + D)
+    eng, norms = run_engine(X, k)
+    assert_matches_oracle(eng, X, norms, k)
+
+
+@pytest.mark.parametrize("N,D,k", [(33, 64, 20), (4097, 128, 300), (2500, 256, 100), (800, 50, 64), (900, 1024, 48)])
+def test_dense_mode_is_bit_identical(N, D, k):
+    X = gaussian_mixture(N, D, 8, seed=N + D)
+    eng, norms = run_engine(X, k, mode=MODE_DENSE)
+    assert_matches_oracle(eng, X, norms, k)
+
+
+def test_reference_parity_script_shape():
+    # data and sizes of the reference's own parity script: 8192 x 32, K = 2048, seed 42
+    X = clustered_jitter(8192, 32, seed=42)
+    eng, norms = run_engine(X, 2048)
+    assert_matches_oracle(eng, X, norms, 2048)
+
+
+def test_exact_ties_take_the_smallest_index():
+    X = with_duplicates(clustered_jitter(3000, 16, seed=5), 600, seed=9)
+    eng, norms = run_engine(X, 1500)
+    assert_matches_oracle(eng, X, norms, 1500)
+
+
+def test_all_rows_identical():
+    X = np.ones((200, 8), dtype=np.float32)
+    eng, norms = run_engine(X, 200)
+    assert_matches_oracle(eng, X, norms, 200)
+    assert eng.selected.cpu().tolist() == list(range(200))
+
+
+def test_seed_picks_and_eager_equals_graph(monkeypatch):
+    X = gaussian_mixture(5000, 64, 8, seed=3)
+    seed = (17, 4000, 123)
+    e1, norms = run_engine(X, 200, seed=seed, graph=True, monkeypatch=monkeypatch)
+    assert_matches_oracle(e1, X, norms, 200, seed=seed)
+    e2, _ = run_engine(X, 200, seed=seed, graph=False, monkeypatch=monkeypatch)
+    assert torch.equal(e1.selected, e2.selected)
+    assert torch.equal(e1.h.view(torch.int32), e2.h.view(torch.int32))
+
+
+def test_public_fps_cuda_api():
+    X_np = gaussian_mixture(6000, 128, 16, seed=1)
+    X = torch.from_numpy(X_np).cuda()
+    sel = fps_mod.fps(X, 256)
+    assert sel.is_cuda and sel.dtype == torch.int64 and sel.shape == (256,)
+    norms = engine.row_norms(X).cpu().numpy()
+    o_sel, _, _, _ = oracle.fps_cuda(X_np, norms, 256)
+    np.testing.assert_array_equal(sel.cpu().numpy(), o_sel)
+    sel2 = fps_mod.fps(X, 64, seed=torch.tensor([5, 9]))
+    o2, _, _, _ = oracle.fps_cuda(X_np, norms, 64, seed=np.array([5, 9]))
+    np.testing.assert_array_equal(sel2.cpu().numpy(), o2)
+    with pytest.raises(ValueError):
+        fps_mod.fps(X.cpu(), 4)
+    with pytest.raises(ValueError):
+        fps_mod.fps(X, 0)
+
+
+def test_prune_evaluates_fewer_rows_than_dense():
+    X = gaussian_mixture(20000, 64, 16, seed=0)
+    dev = torch.device("cuda:0")
+    Xd = torch.from_numpy(X).to(dev)
+    norms = engine.row_norms(Xd)
+    live = {}
+    for mode in (MODE_PRUNE, MODE_DENSE):
+        eng = engine.ShardEngine(Xd, norms, 300, mode=mode)
+        eng.init_state()
+        eng.pick_forced(0)
+        eng.run_picks(298)
+        eng.exchange(); eng.commit(); eng.step()
+        live[mode] = eng.read_ctl().live_rows
+    assert live[MODE_DENSE] == 20000 - 300
+    assert 0 < live[MODE_PRUNE] < live[MODE_DENSE] // 2
+
+
+def test_capacity_overrun_sets_status_not_memory():
+    X = gaussian_mixture(500, 16, 4, seed=2)
+    eng, _ = run_engine(X, 10)
+    eng.run_picks(3)  # beyond cap: kernels refuse, status word records it
+    with pytest.raises(RuntimeError, match="centre table"):
+        eng.check_status()
+
+
+def test_row_norms_chunked_is_bitwise_the_plain_expression(monkeypatch):
+    X = torch.randn(300_000, 64, device="cuda")
+    plain = (X * X).sum(dim=1)
+    monkeypatch.setattr(engine, "_NORM_CHUNK_ELEMS", 64 * 70_000)
+    chunked = engine.row_norms(X)
+    assert torch.equal(plain.view(torch.int32), chunked.view(torch.int32))
+
+
+def _emulate_ranks(X_np, sizes, k, first=0, mode=MODE_PRUNE):
+    """world_size > 1 kernels on ONE device: W engines, the all-gather replaced by copies."""
+    dev = torch.device("cuda:0")
+    W = len(sizes)
+    offs = np.concatenate([[0], np.cumsum(sizes)[:-1]]).tolist()
+    X = torch.from_numpy(X_np).to(dev)
+    norms = engine.row_norms(X)
+    engs = []
+    for r in range(W):
+        Xl = X[offs[r] : offs[r] + sizes[r]].contiguous()
+        nl = norms[offs[r] : offs[r] + sizes[r]].contiguous()
+        e = engine.ShardEngine(Xl, nl, k, shard_offset=offs[r], world_size=W, mode=mode)
+        e.init_state()
+        engs.append(e)
+
+    def gather():
+        allp = torch.stack([e.pack_local for e in engs])
+        for e in engs:
+            e.pack_all.copy_(allp)
+
+    for e in engs:
+        e.force_pick(first)
+    for i in range(k):
+        gather()
+        for e in engs:
+            e.commit()
+            e.step()
+    return engs, norms.cpu().numpy(), offs
+
+
+@pytest.mark.parametrize("sizes", [[1000, 1003], [0, 700, 0, 650], [333] * 7 + [340], [5, 2000]])
+def test_multi_rank_kernels_on_one_device(sizes):
+    N, k = sum(sizes), 150
+    X = with_duplicates(gaussian_mixture(N, 64, 8, seed=N), 50, seed=1)
+    first = N // 2
+    engs, norms, offs = _emulate_ranks(X, sizes, k, first=first)
+    o_sel, o_eps, o_h, o_v = oracle.fps_sharded(X, norms, k, sizes, first=first)
+    for r, e in enumerate(engs):
+        assert e.check_status().n_sel == k
+        np.testing.assert_array_equal(e.selected.cpu().numpy(), o_sel)
+        np.testing.assert_array_equal(bits(e.eps.cpu().numpy()), bits(o_eps))
+        n = sizes[r]
+        np.testing.assert_array_equal(bits(e.h[:n].cpu().numpy()), bits(o_h[offs[r] : offs[r] + n]))
+        np.testing.assert_array_equal(e.voronoi[:n].cpu().numpy().astype(np.int64), o_v[offs[r] : offs[r] + n])
+        assert torch.equal(e.X_sel, engs[0].X_sel)
+
+
+def test_large_shard_properties():
+    """BASELINE-sized shard (the 8-GPU share of the 300M x 128 config: 37.5M rows, 19.2 GB)
+    checked through size-independent properties: unique picks, non-increasing radii, dense and
+    prune modes agreeing, and for sampled rows h == distance to the centre voronoi names, bitwise
+    in the reference's arithmetic."""
+    from coresets_b200.synth import WORKLOADS, MixtureSource, scaled
+    w = scaled(WORKLOADS["c3"], 37_500_000, k=96)
+    dev = torch.device("cuda:0")
+    X = MixtureSource(w).rows(0, w.n_rows, dev)
+    norms = engine.row_norms(X)
+    out = {}
+    for mode in (MODE_PRUNE, MODE_DENSE):
+        eng = engine.ShardEngine(X, norms, w.k, mode=mode)
+        eng.init_state()
+        eng.pick_forced(0)
+        eng.run_picks(w.k - 1)
+        eng.check_status()
+        out[mode] = eng
+    a, b = out[MODE_PRUNE], out[MODE_DENSE]
+    assert torch.equal(a.selected, b.selected)
+    assert torch.equal(a.h.view(torch.int32), b.h.view(torch.int32))
+    assert torch.equal(a.voronoi, b.voronoi)
+    sel = a.selected.cpu().numpy()
+    assert len(set(sel.tolist())) == w.k
+    eps = a.eps.cpu().numpy().astype(np.float64)
+    assert np.isinf(eps[0]) and np.all(eps[2:] <= eps[1:-1] * (1 + 1e-5))
+    g = torch.Generator().manual_seed(0)
+    rows = torch.randint(0, w.n_rows, (2048,), generator=g)
+    Xs = X[rows.to(dev)].cpu().numpy()
+    hs = a.h[rows.to(dev)].cpu().numpy()
+    vs = a.voronoi[rows.to(dev)].cpu().numpy()
+    ns = norms[rows.to(dev)].cpu().numpy()
+    Xsel = a.X_sel.cpu().numpy()
+    nsel = a.norms_sel.cpu().numpy()
+    for j in range(rows.numel()):
+        if hs[j] < 0:
+            continue
+        dot = np.float32(oracle.warp_dot(Xs[j], Xsel[vs[j]]))
+        d = np.float32(np.float32(ns[j] + nsel[vs[j]]) - np.float32(dot + dot))
+        assert bits(d) == bits(hs[j])
+    # the nearest centre in float64 agrees with voronoi up to rounding
+    d64 = ((Xs[:256, None, :].astype(np.float64) - Xsel[None].astype(np.float64)) ** 2).sum(-1)
+    near = d64.min(axis=1)
+    mine = d64[np.arange(256), vs[:256]]
+    assert np.all(mine <= near * (1 + 1e-4) + 1e-6)
