@@ -253,3 +253,37 @@ def test_large_shard_properties():
     near = d64.min(axis=1)
     mine = d64[np.arange(256), vs[:256]]
     assert np.all(mine <= near * (1 + 1e-4) + 1e-6)
+
+
+# ---- golden vectors written by the reference's own CUDA extension on a B200 ----------------------
+from pathlib import Path  # noqa: E402
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+GOLDEN_CASES = sorted(p.stem for p in GOLDEN.glob("*.npz") if p.stem != "cpu_fps_c1")
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_engine_reproduces_reference_golden(name):
+    from tests.test_oracle_golden import load_case
+    z, X = load_case(name)
+    K = int(z["K"])
+    seeds = tuple(int(s) for s in z["seeds"])
+    eng, norms = run_engine(X, K, seed=seeds)
+    np.testing.assert_array_equal(bits(norms), bits(z["norms"]))      # torch norms, same GPU type
+    np.testing.assert_array_equal(eng.selected.cpu().numpy(), z["selected"])
+    np.testing.assert_array_equal(bits(eng.eps.cpu().numpy()), bits(z["eps"]))
+    np.testing.assert_array_equal(bits(eng.h[: X.shape[0]].cpu().numpy()), bits(z["h"]))
+    np.testing.assert_array_equal(eng.voronoi[: X.shape[0]].cpu().numpy(), z["voronoi"])
+
+
+@pytest.mark.parametrize("wname,n_rows", [("c3", 2_000_000), ("c2", 5_000_000), ("c4", 400_000), ("c3", 37_500_000)])
+def test_engine_reproduces_reference_on_device_generated_workloads(wname, n_rows):
+    """`selected` of the reference's fps_cuda on scaled-down benchmark workloads (matrices
+    generated on the device, so only a B200 with this torch build regenerates them)."""
+    from coresets_b200.synth import WORKLOADS, MixtureSource, scaled
+    ref = np.load(GOLDEN / f"midsize_{wname}_{n_rows}_selected.npy")
+    K = ref.shape[0]
+    w = scaled(WORKLOADS[wname], n_rows, k=K)
+    X = MixtureSource(w).rows(0, n_rows, torch.device("cuda:0"))
+    sel = fps_mod.fps(X, K)
+    np.testing.assert_array_equal(sel.cpu().numpy(), ref)
