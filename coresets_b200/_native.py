@@ -25,7 +25,7 @@ RULE_SIM_SHARDED = 2
 EXPORTS = (
     "cs_version", "cs_error_string", "cs_last_cuda_error", "cs_device_check", "cs_init_state",
     "cs_reset_ctl", "cs_force_pick", "cs_commit_bound", "cs_fps_step", "cs_sim_begin",
-    "cs_sim_final_check", "cs_fps_step_lanes",
+    "cs_sim_final_check", "cs_fps_step_lanes", "cs_fps_step_noalloc",
 )
 
 
@@ -112,6 +112,9 @@ class Native:
             fn = getattr(L, name)
             fn.restype = ctypes.c_int
             fn.argtypes = args
+        L.cs_fps_step_noalloc.restype = ctypes.c_int
+        L.cs_fps_step_noalloc.argtypes = [vp, vp, vp, vp, ctypes.c_int64, ctypes.c_int32, ctypes.c_int64, vp,
+                                          ctypes.c_float, vp, ctypes.c_int32, ctypes.c_uint32, vp, vp, vp]
         if L.cs_version() != CS_ABI_VERSION:
             raise NativeError(f"{lib_path}: ABI {L.cs_version()} != expected {CS_ABI_VERSION}; rebuild it")
 
@@ -148,6 +151,15 @@ class Native:
 
     def sim_final_check(self, s: CsState, stream: int) -> None:
         self._check(self.lib.cs_sim_final_check(ctypes.byref(s), stream), "cs_sim_final_check")
+
+    def fps_step_noalloc(self, X: int, norms: int, h: int, voronoi: int, N_local: int, D: int,
+                         shard_offset: int, centre: int, norm_new: float, dSL: Optional[int], sel_pos: int,
+                         mode: int, out_key: int, out_live_rows: Optional[int], stream: int) -> None:
+        """``cs_fps_step_noalloc``: the fused step for hosts that may not allocate device memory;
+        every pointer argument is a raw device address.  Raises on a non-zero return code."""
+        self._check(self.lib.cs_fps_step_noalloc(X, norms, h, voronoi, N_local, D, shard_offset, centre,
+                                                 norm_new, dSL, sel_pos, mode, out_key, out_live_rows, stream),
+                    "cs_fps_step_noalloc")
 
     def fps_step_lanes(self, lanes, n_lanes: int, mode: int, stream: int) -> None:
         self._check(self.lib.cs_fps_step_lanes(lanes, n_lanes, mode, stream), "cs_fps_step_lanes")

@@ -510,6 +510,7 @@ const char* cs_error_string(int code) {
         case CS_E_RANGE: return "global row index space or capacity must stay below 2^31";
         case CS_E_LAUNCH: return "CUDA launch failed (see cs_last_cuda_error)";
         case CS_E_DEVICE: return "no CUDA device of compute capability 10.x is current";
+        case CS_E_SCRATCH: return "row length exceeds CS_NOALLOC_MAX_D, the fixed scratch of cs_fps_step_noalloc";
         default: return "unknown error code";
     }
 }
@@ -619,3 +620,109 @@ int cs_fps_step_lanes(const cs_state* lanes, int32_t n_lanes, uint32_t mode, cs_
 }
 
 }  // extern "C"
+
+// ---- allocation-free variant of the fused step -------------------------------------------------
+// Some hosts of this library own every byte of device memory themselves and may not call
+// cudaMalloc once they are running: a process that handed the whole HBM to its own arena when it
+// started (a 150 GB matrix leaves little else), or a plug-in loaded into a service whose policy
+// forbids driver allocations -- and the device-wide stall they cause -- on the request path.
+// For them the scratch the step needs (the 256-byte control block plus a one-row centre table)
+// lives in the fixed array below instead of in caller-allocated buffers.  Every GPU that loads
+// the library holds these CS_NOALLOC_SCRATCH_BYTES until the process exits.
+#define CS_NOALLOC_SCRATCH_BYTES (CS_CTL_BYTES + 256 + CS_NOALLOC_MAX_D * 4)
+static __device__ __align__(256) unsigned char g_noalloc_scratch[CS_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+unsigned char* g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+// Device address of g_noalloc_scratch on the CURRENT device.  In host code the array's name is
+// only a handle; the address a kernel can use comes from cudaGetSymbolAddress, asked once per
+// device while that device is current.
+int noalloc_scratch(unsigned char** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return CS_E_DEVICE;
+    if (!g_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            g_last_cuda = e;
+            return CS_E_LAUNCH;
+        }
+        g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+    }
+    *out = g_noalloc_ptr[dev];
+    return CS_OK;
+}
+
+// The scratch keeps whatever the previous call left: zero the control block, then stage this
+// call's centre (row + norm) and pick position.
+__global__ void noalloc_prepare_kernel(unsigned char* scratch, const float* __restrict__ centre,
+                                       const float norm_new, const int D, const int sel_pos) {
+    Ctl* ctl = reinterpret_cast<Ctl*>(scratch);
+    float* norm_slot = reinterpret_cast<float*>(scratch + CS_CTL_BYTES);
+    float* row_slot = reinterpret_cast<float*>(scratch + CS_CTL_BYTES + 256);
+    if (threadIdx.x < CS_CTL_BYTES / 4) reinterpret_cast<uint32_t*>(ctl)[threadIdx.x] = 0u;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) row_slot[c] = centre[c];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        ctl->n_sel = sel_pos;
+        norm_slot[0] = norm_new;
+    }
+}
+
+__global__ void noalloc_publish_kernel(const unsigned char* scratch, const int sel_pos, u64* out_key,
+                                       u64* out_live_rows) {
+    const Ctl* ctl = reinterpret_cast<const Ctl*>(scratch);
+    if (out_key) *out_key = ctl->key[(sel_pos + 1) & 1];
+    if (out_live_rows) *out_live_rows = ctl->live_rows;
+}
+
+}  // namespace
+
+extern "C" int cs_fps_step_noalloc(const float* X, const float* norms, float* h, int32_t* voronoi,
+                                   int64_t N_local, int32_t D, int64_t shard_offset, const float* centre,
+                                   float norm_new, const float* dSL_quarter, int32_t sel_pos, uint32_t mode,
+                                   uint64_t* out_key, uint64_t* out_live_rows, cs_stream stream) {
+    if (!X || !norms || !h || !voronoi || !centre || !out_key) return CS_E_ARG;
+    if (N_local <= 0 || D <= 0 || sel_pos < 0 || shard_offset < 0 || mode > CS_MODE_DENSE) return CS_E_ARG;
+    if (sel_pos > 0 && !dSL_quarter) return CS_E_ARG;
+    if (D > CS_NOALLOC_MAX_D) return CS_E_SCRATCH;        // the centre would not fit the fixed scratch
+    unsigned char* scratch = nullptr;
+    int rc = noalloc_scratch(&scratch);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+
+    // A one-row centre table whose slot `sel_pos` is the staged row: the step kernel indexes
+    // X_sel / norms_sel by the pick position, so the bases are set sel_pos rows before the slot.
+    cs_state s;
+    s.X = X;
+    s.norms = norms;
+    s.h = h;
+    s.voronoi = voronoi;
+    s.N_local = N_local;
+    s.shard_offset = shard_offset;
+    s.D = D;
+    s.world_size = 1;
+    const uintptr_t row_slot = (uintptr_t)(scratch + CS_CTL_BYTES + 256);
+    const uintptr_t norm_slot = (uintptr_t)(scratch + CS_CTL_BYTES);
+    s.X_sel = reinterpret_cast<float*>(row_slot - (uintptr_t)sel_pos * (uintptr_t)D * sizeof(float));
+    s.norms_sel = reinterpret_cast<float*>(norm_slot - (uintptr_t)sel_pos * sizeof(float));
+    s.dSL_quarter = const_cast<float*>(dSL_quarter ? dSL_quarter : reinterpret_cast<const float*>(norm_slot));
+    s.cap = (int64_t)sel_pos + 1;
+    s.selected = nullptr;
+    s.eps = nullptr;
+    s.ctl = scratch;
+    s.pack_local = nullptr;
+    s.pack_all = nullptr;
+
+    noalloc_prepare_kernel<<<1, 256, 0, st>>>(scratch, centre, norm_new, D, sel_pos);
+    rc = check_launch();
+    if (rc) return rc;
+    rc = cs_fps_step(&s, mode, stream);
+    if (rc) return rc;
+    noalloc_publish_kernel<<<1, 1, 0, st>>>(scratch, sel_pos, reinterpret_cast<u64*>(out_key),
+                                            reinterpret_cast<u64*>(out_live_rows));
+    return check_launch();
+}

@@ -46,6 +46,7 @@ extern "C" {
 #define CS_E_RANGE (-3)    /* global index space >= 2^31, or a size above a stated maximum */
 #define CS_E_LAUNCH (-4)   /* the CUDA runtime refused the launch (see cs_last_cuda_error) */
 #define CS_E_DEVICE (-5)   /* no usable sm_100 device / wrong architecture */
+#define CS_E_SCRATCH (-6)  /* D exceeds CS_NOALLOC_MAX_D, the fixed scratch of cs_fps_step_noalloc */
 
 /* cs_fps_step flags */
 #define CS_MODE_PRUNE 0u   /* rows excluded by the triangle bound are not loaded (default) */
@@ -174,6 +175,37 @@ CS_API int cs_sim_final_check(const cs_state* s, cs_stream stream);
  * Replaces voronoi_update_lanes_kernel (kernels/multi.cu:569-708).
  */
 CS_API int cs_fps_step_lanes(const cs_state* lanes, int32_t n_lanes, uint32_t mode, cs_stream stream);
+
+/*
+ * cs_fps_step without any caller-provided scratch and without any allocation.  No counterpart
+ * in the reference.
+ *
+ * For hosts that cannot allocate device memory while they run -- a process that gave the whole
+ * HBM to its own arena at start-up, or a plug-in inside a service that forbids driver
+ * allocations (and the device-wide stall they cause) on its request path.  The control block
+ * and the centre slot that cs_fps_step normally finds in caller buffers live in a fixed
+ * per-device array inside the library (256 + 256 + 4 * CS_NOALLOC_MAX_D bytes, held by every GPU
+ * that loads the library until the process exits).  The call makes no cudaMalloc / cudaFree and
+ * uses no allocating library routine.
+ *
+ * Inputs: X, norms, h, voronoi as in cs_state; `centre` = the D floats of the new centre,
+ * `norm_new` its squared norm, `sel_pos` its position in the selection (written into voronoi;
+ * 0 selects the dense first-centre update), `dSL_quarter` = sel_pos triangle bounds (may be NULL
+ * when sel_pos == 0).  Outputs: h / voronoi updated in place; *out_key = the arg-max key of the
+ * next pick (value-orderable bits << 32 | 0xFFFFFFFF - global index, 0 = no candidate);
+ * *out_live_rows (optional) = rows whose distance was evaluated.  All pointers are device
+ * pointers.  D above CS_NOALLOC_MAX_D returns CS_E_SCRATCH.
+ *
+ * The first call on a device looks up the array's device address (a synchronous runtime query):
+ * make that call before starting any stream capture.  Every call on a device shares the one
+ * array, which keeps the previous call's contents; each call clears what must start at zero, but
+ * two calls that overlap on the GPU (different streams, no ordering) race on it.
+ */
+#define CS_NOALLOC_MAX_D 4096
+CS_API int cs_fps_step_noalloc(const float* X, const float* norms, float* h, int32_t* voronoi,
+                               int64_t N_local, int32_t D, int64_t shard_offset, const float* centre,
+                               float norm_new, const float* dSL_quarter, int32_t sel_pos, uint32_t mode,
+                               uint64_t* out_key, uint64_t* out_live_rows, cs_stream stream);
 
 #ifdef __cplusplus
 }
