@@ -293,7 +293,11 @@ def run_ours(args):
     if not args.no_e2e:
         del eng, norms
         torch.cuda.empty_cache()
-        e2e = run_e2e(args, X, w, world, rank, device, K, W, off)
+        try:
+            e2e = run_e2e(args, X, w, world, rank, device, K, W, off)
+        except Exception as ex:  # the headline line must still print
+            e2e = {"value": None, "unit": UNIT, "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
+                   "error": f"{type(ex).__name__}: {str(ex)[:200]}"}
 
     cpu_b = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -324,25 +328,84 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+class HostMatrix:
+    """Host-side copy of a rank's rows.  Fully page-locked when the machine allows it; otherwise
+    ordinary pageable memory that is moved through a ring of two page-locked staging buffers
+    (CPU copy of chunk i+1 overlaps the DMA of chunk i), the way a user's large numpy array
+    reaches the device."""
+    RING_BYTES = 1 << 30
+
+    def __init__(self, X: torch.Tensor):
+        self.shape, self.dtype = tuple(X.shape), X.dtype
+        self.pinned = True
+        try:
+            self.host = torch.empty(self.shape, dtype=self.dtype, pin_memory=True)
+        except Exception:
+            self.pinned = False
+            torch.cuda.synchronize(X.device)
+            self.host = torch.empty(self.shape, dtype=self.dtype)
+        self.ring = None
+        if not self.pinned:
+            rows = max(1, self.RING_BYTES // max(1, self.shape[1] * 4))
+            self.ring = [torch.empty((rows, self.shape[1]), dtype=self.dtype, pin_memory=True) for _ in range(2)]
+        self._move(X, to_device=False)
+
+    def _move(self, X: torch.Tensor, to_device: bool) -> None:
+        if self.pinned:
+            (X.copy_(self.host, non_blocking=True) if to_device else self.host.copy_(X, non_blocking=True))
+            if not to_device:
+                torch.cuda.synchronize(X.device)
+            return
+        rows = self.ring[0].shape[0]
+        evs = [None, None]
+        n = self.shape[0]
+        pending = None
+        for i, a in enumerate(range(0, n, rows)):
+            b = min(a + rows, n)
+            buf = self.ring[i % 2]
+            if evs[i % 2] is not None:
+                evs[i % 2].synchronize()
+            if to_device:
+                buf[: b - a].copy_(self.host[a:b])
+                X[a:b].copy_(buf[: b - a], non_blocking=True)
+            else:
+                if pending is not None:          # drain the previous chunk while this one flies
+                    pa, pb, pbuf, pev = pending
+                    pev.synchronize()
+                    self.host[pa:pb].copy_(pbuf[: pb - pa])
+                buf[: b - a].copy_(X[a:b], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            evs[i % 2] = ev
+            if not to_device:
+                pending = (a, b, buf, ev)
+        if not to_device and pending is not None:
+            pa, pb, pbuf, pev = pending
+            pev.synchronize()
+            self.host[pa:pb].copy_(pbuf[: pb - pa])
+
+    def upload(self, X: torch.Tensor) -> None:
+        self._move(X, to_device=True)
+
+
 def run_e2e(args, X, w, world, rank, device, K, W, off):
-    """One complete job through the public API shape: pinned host X -> H2D -> norms -> first pick ->
-    K picks -> D2H of (selected, epsilons).  The W warm-up picks between the load phase and the K
-    timed picks are not counted.  Returns None (with the reason) when the host cannot pin X."""
+    """One complete job through the engine from HOST rows: H2D of the rank's rows -> norms -> first
+    pick -> K picks -> D2H of (selected, epsilons).  The W warm-up picks between the load phase and
+    the K timed picks are not counted.  The one-off upload is charged in full to the K picks."""
     from coresets_b200 import engine
     from coresets_b200._native import MODE_DENSE
     import psutil
     n_local, dim = X.shape
     nbytes = n_local * dim * 4
     avail = psutil.virtual_memory().available
-    ok = torch.tensor([1 if nbytes * 1.10 + (8 << 30) < avail / max(1, min(world, torch.cuda.device_count())) else 0],
-                      device=device)
+    share = max(1, min(world, torch.cuda.device_count()))
+    ok = torch.tensor([1 if nbytes + (16 << 30) / share < avail / share else 0], device=device)
     if world > 1:
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if int(ok.item()) == 0:
         return {"value": None, "unit": UNIT, "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
-                "skipped": f"host cannot pin {nbytes/1e9:.1f} GB per rank ({avail/1e9:.1f} GB available)"}
-    host = torch.empty((n_local, dim), dtype=torch.float32, pin_memory=True)
-    host.copy_(X)
+                "skipped": f"host memory: {nbytes/1e9:.1f} GB per rank needed, {avail/1e9:.1f} GB available"}
+    hm = HostMatrix(X)
     torch.cuda.synchronize(device)
     sel_host = torch.empty(1 + W + K, dtype=torch.int64, pin_memory=True)
     eps_host = torch.empty(1 + W + K, dtype=torch.float32, pin_memory=True)
@@ -350,12 +413,15 @@ def run_e2e(args, X, w, world, rank, device, K, W, off):
     e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
     barrier_sync(device)
     e[0].record()
-    X.copy_(host, non_blocking=True)
+    t_host0 = time.perf_counter()
+    hm.upload(X)
     norms = engine.row_norms(X)
     eng2 = engine.ShardEngine(X, norms, 1 + W + K, shard_offset=off, world_size=world, mode=MODE_DENSE)
     eng2.init_state()
     eng2.pick_forced(0)
     e[1].record()
+    e[1].synchronize()
+    load_wall_ms = 1e3 * (time.perf_counter() - t_host0)
     eng2.prepare(K)
     eng2.run_picks(W)
     barrier_sync(device)
@@ -365,14 +431,19 @@ def run_e2e(args, X, w, world, rank, device, K, W, off):
     eps_host.copy_(eng2.eps, non_blocking=True)
     e[3].record()
     barrier_sync(device)
-    load_ms = dist_max(e[0].elapsed_time(e[1]), device)
+    load_ms = dist_max(max(e[0].elapsed_time(e[1]), load_wall_ms), device)
     picks_ms = dist_max(e[2].elapsed_time(e[3]), device)
     eng2.check_status()
     total_s = (load_ms + picks_ms) / 1e3
+    k_job = w.k
     return {"value": K / total_s, "unit": UNIT, "h2d_bytes_per_step": nbytes * world / K,
             "d2h_bytes_per_step": 12.0 * (1 + W + K) / K, "load_ms": load_ms, "picks_ms": picks_ms,
-            "what": f"one job of {K} picks: pinned-host X -> device ({nbytes/1e9:.1f} GB per rank), norms, first "
-                    f"pick, {K} picks, read-back of selected/epsilons; H2D amortised over the {K} picks"}
+            "host_memory": "page-locked" if hm.pinned else "pageable, staged through two 1 GiB page-locked buffers",
+            "h2d_gb_per_s": nbytes / 1e9 / (load_ms / 1e3),
+            "full_job_estimate": {"value": 1.0 / (load_ms / 1e3 / k_job + picks_ms / 1e3 / K), "unit": UNIT,
+                                  "how": f"derived, not measured: the same upload amortised over the config's k={k_job} picks"},
+            "what": f"one job of {K} picks: host rows -> device ({nbytes/1e9:.1f} GB per rank), norms, first pick, "
+                    f"{K} picks, read-back of selected/epsilons; the whole upload is charged to the {K} picks"}
 
 
 def main():

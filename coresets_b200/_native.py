@@ -25,7 +25,7 @@ RULE_SIM_SHARDED = 2
 EXPORTS = (
     "cs_version", "cs_error_string", "cs_last_cuda_error", "cs_device_check", "cs_init_state",
     "cs_reset_ctl", "cs_force_pick", "cs_commit_bound", "cs_fps_step", "cs_sim_begin",
-    "cs_sim_final_check", "cs_fps_step_lanes", "cs_fps_step_noalloc",
+    "cs_sim_final_check", "cs_scan_argmax", "cs_fps_step_lanes", "cs_fps_step_noalloc",
 )
 
 
@@ -107,6 +107,7 @@ class Native:
             ("cs_fps_step", [sp, ctypes.c_uint32, vp]),
             ("cs_sim_begin", [sp, ctypes.c_float, vp]),
             ("cs_sim_final_check", [sp, vp]),
+            ("cs_scan_argmax", [sp, vp]),
             ("cs_fps_step_lanes", [sp, ctypes.c_int32, ctypes.c_uint32, vp]),
         ):
             fn = getattr(L, name)
@@ -151,6 +152,9 @@ class Native:
 
     def sim_final_check(self, s: CsState, stream: int) -> None:
         self._check(self.lib.cs_sim_final_check(ctypes.byref(s), stream), "cs_sim_final_check")
+
+    def scan_argmax(self, s: CsState, stream: int) -> None:
+        self._check(self.lib.cs_scan_argmax(ctypes.byref(s), stream), "cs_scan_argmax")
 
     def fps_step_noalloc(self, X: int, norms: int, h: int, voronoi: int, N_local: int, D: int,
                          shard_offset: int, centre: int, norm_new: float, dSL: Optional[int], sel_pos: int,

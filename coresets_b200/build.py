@@ -16,7 +16,7 @@ from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
-LIB = PKG / "libcoresets_b200.so"
+LIB = Path(os.environ["CORESETS_B200_LIB"]) if os.environ.get("CORESETS_B200_LIB") else PKG / "libcoresets_b200.so"
 SOURCES = [PKG / "csrc" / "fps_kernels.cu"]
 HEADERS = [ROOT / "include" / "coresets_b200.h"]
 
@@ -46,7 +46,7 @@ def needs_build() -> bool:
 def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not needs_build():
         return LIB
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(ROOT / "include")]
+    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(ROOT / "include"), *os.environ.get("CORESETS_B200_NVCC_DEFS", "").split()]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", str(LIB), *map(str, SOURCES)]

@@ -38,6 +38,14 @@ enum { ST_CAPACITY = 1, ST_FORCE_NOT_OWNED = 2 };
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr unsigned kFull = 0xffffffffu;
+constexpr int kRowsPerLane = 4;          // a warp walks super-tiles of 32 * 4 = 128 consecutive rows
+#ifndef CS_INFLIGHT
+#define CS_INFLIGHT 8
+#endif
+#ifndef CS_MIN_BLOCKS
+#define CS_MIN_BLOCKS 3                  // resident blocks per SM the step kernel is compiled for
+#endif
+constexpr int kInflight = CS_INFLIGHT;   // independent 16-byte row loads per lane in flight
 
 thread_local cudaError_t g_last_cuda = cudaSuccess;
 
@@ -210,16 +218,17 @@ __global__ void __launch_bounds__(kThreads) commit_bound_kernel(const cs_state s
 }
 
 // ---- kernel B: fused distance + min-update + arg-max ---------------------------------------
-// A warp owns tiles of 32 consecutive rows: lane j holds h / voronoi / norm of row base+j
-// (coalesced), the warp then walks the rows that need a distance, RB rows per batch so that
-// RB * CPL 16-byte loads per lane are in flight, every row read with one fully coalesced
+// A warp owns super-tiles of 128 consecutive rows: lane j holds h / voronoi of rows base+4j..4j+3
+// (one 16-byte load each, coalesced), the warp then walks the rows that need a distance, RB rows
+// per batch so that RB * CPL 16-byte loads per lane are in flight, every row read with one fully coalesced
 // 512-byte (or wider) request.  CPL = float4 chunks per lane = ceil(D / 128); CPL == 0 is the
 // generic path (any D, centre in shared memory).
 template <int CPL, bool FULL>
 __device__ __forceinline__ void tile_rows(const float4* __restrict__ X4, const int64_t base,
                                           const int d4, unsigned m, const float4 (&cen)[CPL ? CPL : 1],
                                           const int lane, float& mydot) {
-    constexpr int RB = CPL >= 8 ? 1 : (8 / (CPL ? CPL : 1));
+    // bit r of m stands for row base + kRowsPerLane * r (lane r's sub-row)
+    constexpr int RB = CPL >= kInflight ? 1 : (kInflight / (CPL ? CPL : 1));
     while (m) {
         int rows[RB];
         float4 a[RB][CPL ? CPL : 1];
@@ -231,7 +240,7 @@ __device__ __forceinline__ void tile_rows(const float4* __restrict__ X4, const i
 #pragma unroll
         for (int b = 0; b < RB; ++b) {
             if (rows[b] >= 0) {
-                const float4* rp = X4 + (base + rows[b]) * (int64_t)d4 + lane;
+                const float4* rp = X4 + (base + (int64_t)rows[b] * kRowsPerLane) * (int64_t)d4 + lane;
 #pragma unroll
                 for (int c = 0; c < CPL; ++c)
                     if (FULL || lane + 32 * c < d4) a[b][c] = ld_stream4(rp + 32 * c);
@@ -252,7 +261,7 @@ __device__ __forceinline__ void tile_rows(const float4* __restrict__ X4, const i
 }
 
 template <int CPL, bool FULL>
-__global__ void __launch_bounds__(kThreads) fps_step_kernel(const cs_state s, const unsigned mode) {
+__global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const cs_state s, const unsigned mode) {
     extern __shared__ __align__(16) float s_cen[];       // generic path only
     __shared__ u64 s_keys[kWarps];
     __shared__ unsigned s_live[kWarps];
@@ -285,51 +294,99 @@ __global__ void __launch_bounds__(kThreads) fps_step_kernel(const cs_state s, co
     }
 
     const int64_t N = s.N_local;
-    const int64_t tiles = (N + 31) >> 5;
+    const int64_t tiles = (N + 127) >> 7;
     const int64_t nw = (int64_t)gridDim.x * kWarps;
     const float4* X4 = reinterpret_cast<const float4*>(s.X);
+    const bool vec_ok = ((((uintptr_t)s.h) | ((uintptr_t)s.voronoi) | ((uintptr_t)s.norms)) & 15u) == 0;
     u64 best = 0;
     unsigned live_cnt = 0;
 
     for (int64_t t = (int64_t)blockIdx.x * kWarps + warp; t < tiles; t += nw) {
-        const int64_t base = t << 5;
-        const int64_t row = base + lane;
-        const bool valid = row < N;
-        float hj = valid ? s.h[row] : -1.0f;
-        const bool live = valid && !(hj < 0.0f);                 // warp.cu:28-30, 75-77
-        bool upd = live;
-        if (live && !first) {
-            const int vj = s.voronoi[row];
-            if (__ldg(s.dSL_quarter + vj) >= hj) upd = false;    // warp.cu:80-82
-        }
-        const bool need = dense ? live : upd;
-        const unsigned m = __ballot_sync(kFull, need);
-        live_cnt += __popc(m);
-        float mydot = 0.0f;
-        if (m) {
-            if (CPL) {
-                tile_rows<CPL, FULL>(X4, base, d4, m, cen, lane, mydot);
+        // lane j owns rows r0 .. r0+3: one 16-byte load each for h and voronoi (coalesced 512 B)
+        const int64_t base = t << 7;
+        const int64_t r0 = base + 4 * lane;
+        float hq[4];
+        unsigned updbits = 0;                // bit j: row r0+j may be updated
+        unsigned m[4];
+        const bool whole = vec_ok && (r0 + 3 < N);
+        {
+            int vq[4] = {0, 0, 0, 0};
+            if (whole) {
+                const float4 h4 = *reinterpret_cast<const float4*>(s.h + r0);
+                hq[0] = h4.x; hq[1] = h4.y; hq[2] = h4.z; hq[3] = h4.w;
+                if (!first) {
+                    const int4 v4 = *reinterpret_cast<const int4*>(s.voronoi + r0);
+                    vq[0] = v4.x; vq[1] = v4.y; vq[2] = v4.z; vq[3] = v4.w;
+                }
             } else {
-                unsigned mm = m;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const bool in = r0 + j < N;
+                    hq[j] = in ? s.h[r0 + j] : -1.0f;
+                    vq[j] = (in && !first) ? s.voronoi[r0 + j] : 0;
+                }
+            }
+            float bound[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const bool live = (r0 + j < N) && !(hq[j] < 0.0f);        // warp.cu:28-30, 75-77
+                bound[j] = (live && !first) ? __ldg(s.dSL_quarter + vq[j]) : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const bool live = (r0 + j < N) && !(hq[j] < 0.0f);
+                const bool up = live && (first || !(bound[j] >= hq[j]));   // warp.cu:80-82
+                updbits |= (up ? 1u : 0u) << j;
+                m[j] = __ballot_sync(kFull, dense ? live : up);
+                live_cnt += __popc(m[j]);
+            }
+        }
+        float dots[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j) {       // one copy of the row walk, not four (register budget)
+            const unsigned mj = j == 0 ? m[0] : j == 1 ? m[1] : j == 2 ? m[2] : m[3];
+            if (!mj) continue;
+            float dj = 0.0f;
+            if (CPL) {
+                tile_rows<CPL, FULL>(X4, base + j, d4, mj, cen, lane, dj);
+            } else {
+                unsigned mm = mj;
                 while (mm) {
                     const int r = __ffs(mm) - 1;
                     mm &= mm - 1;
-                    float p = warp_dot_generic(s.X + (base + r) * (int64_t)D, s_cen, D, lane);
-                    if (lane == r) mydot = p;
+                    float p = warp_dot_generic(s.X + (base + j + (int64_t)r * kRowsPerLane) * (int64_t)D, s_cen, D, lane);
+                    if (lane == r) dj = p;
+                }
+            }
+            if (j == 0) dots[0] = dj; else if (j == 1) dots[1] = dj; else if (j == 2) dots[2] = dj; else dots[3] = dj;
+        }
+        if (updbits) {
+            float nq[4];
+            if (whole && dense) {
+                const float4 n4 = __ldg(reinterpret_cast<const float4*>(s.norms + r0));
+                nq[0] = n4.x; nq[1] = n4.y; nq[2] = n4.z; nq[3] = n4.w;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) nq[j] = ((updbits >> j) & 1u) ? __ldg(s.norms + r0 + j) : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if ((updbits >> j) & 1u) {
+                    const float d = sq_dist(nq[j], nn, dots[j]);
+                    if (d < hq[j]) {
+                        hq[j] = d;
+                        s.h[r0 + j] = d;
+                        s.voronoi[r0 + j] = i;
+                    }
                 }
             }
         }
-        if (upd) {
-            const float d = sq_dist(__ldg(s.norms + row), nn, mydot);
-            if (d < hj) {
-                hj = d;
-                s.h[row] = d;
-                s.voronoi[row] = i;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (r0 + j < N) {
+                const u64 k = make_key(hq[j], s.shard_offset + r0 + j);
+                best = k > best ? k : best;
             }
-        }
-        if (valid) {
-            const u64 k = make_key(hj, s.shard_offset + row);
-            best = k > best ? k : best;
         }
     }
 
@@ -423,6 +480,53 @@ __global__ void sim_final_check_kernel(const cs_state s) {
     if (ctl->sep > key_val(w.key)) ctl->viable = 1;   // argmax.cu:152-159, multi.cu:369-384
 }
 
+// ---- arg-max only: recompute the key of the NEXT pick from the current h --------------------
+// Needed whenever h was changed behind the step kernel's back (roll-back to a snapshot, a
+// reconstructed bisect state) and for "global max h" queries.  Same key, same pack as fps_step.
+__global__ void scan_reset_kernel(Ctl* ctl) { ctl->key[ctl->n_sel & 1] = 0; }
+
+__global__ void __launch_bounds__(kThreads) scan_argmax_kernel(const cs_state s) {
+    __shared__ u64 s_keys[kWarps];
+    __shared__ int s_last;
+    Ctl* ctl = reinterpret_cast<Ctl*>(s.ctl);
+    const int slot = ctl->n_sel & 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    u64 best = 0;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < s.N_local; r += stride) {
+        const u64 k = make_key(s.h[r], s.shard_offset + r);
+        best = k > best ? k : best;
+    }
+    best = warp_max_key(best);
+    if (lane == 0) s_keys[warp] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        u64 bk = 0;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) bk = s_keys[w] > bk ? s_keys[w] : bk;
+        if (bk) atomicMax(&ctl->key[slot], bk);
+        __threadfence();
+        s_last = (atomicAdd(&ctl->ticket, 1u) == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const u64 k = *reinterpret_cast<volatile u64*>(&ctl->key[slot]);
+    if (s.world_size > 1) {
+        uint32_t* p = s.pack_local;
+        const int64_t l = key_idx(k) - s.shard_offset;
+        if (threadIdx.x == 0) {
+            p[0] = (uint32_t)(k & 0xffffffffu);
+            p[1] = (uint32_t)(k >> 32);
+            p[2] = k ? __float_as_uint(s.norms[l]) : 0u;
+            p[3] = 0u;
+        }
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(s.X + (k ? l : 0) * (int64_t)s.D);
+        for (int c = threadIdx.x; c < s.D; c += blockDim.x) p[4 + c] = k ? src[c] : 0u;
+    }
+    if (threadIdx.x == 0) ctl->ticket = 0;
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 struct DevInfo {
     int sms = 0;
@@ -488,7 +592,7 @@ int launch_step(const cs_state* s, unsigned mode, cudaStream_t st, int sms) {
         }
         if (CPL) bps = per_sm;
     }
-    const int64_t tiles = (s->N_local + 31) >> 5;
+    const int64_t tiles = (s->N_local + 127) >> 7;
     int64_t want = (tiles + kWarps - 1) / kWarps;
     int64_t cap = (int64_t)sms * per_sm;         // persistent grid: a multiple of the SM count
     int grid = (int)(want < 1 ? 1 : (want < cap ? want : cap));
@@ -606,6 +710,22 @@ int cs_sim_final_check(const cs_state* s, cs_stream stream) {
     int rc = validate(s);
     if (rc) return rc;
     sim_final_check_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(*s);
+    return check_launch();
+}
+
+int cs_scan_argmax(const cs_state* s, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    DevInfo d = device_info();
+    if (!d.ok) return CS_E_DEVICE;
+    cudaStream_t st = (cudaStream_t)stream;
+    scan_reset_kernel<<<1, 1, 0, st>>>(reinterpret_cast<Ctl*>(s->ctl));
+    rc = check_launch();
+    if (rc) return rc;
+    int64_t want = (s->N_local + 4 * kThreads - 1) / (4 * kThreads);
+    int64_t lim = (int64_t)d.sms * 8;
+    int grid = (int)(want < 1 ? 1 : (want < lim ? want : lim));
+    scan_argmax_kernel<<<grid, kThreads, 0, st>>>(*s);
     return check_launch();
 }
 

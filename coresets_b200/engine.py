@@ -155,6 +155,16 @@ class ShardEngine:
         if self.world_size > 1:
             dist.all_gather_into_tensor(self.pack_all.view(-1), self.pack_local, group=self.group)
 
+    def scan(self) -> None:
+        """Recompute the next pick's key (and pack) from the current ``h``."""
+        self.native.scan_argmax(self.state, self._stream())
+
+    def sim_begin(self, sep: float) -> None:
+        self.native.sim_begin(self.state, float(sep), self._stream())
+
+    def sim_final_check(self) -> None:
+        self.native.sim_final_check(self.state, self._stream())
+
     def commit(self, rules: int = RULE_NONE) -> None:
         self.native.commit_bound(self.state, int(rules), self._stream())
 

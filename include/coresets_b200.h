@@ -169,6 +169,15 @@ CS_API int cs_sim_begin(const cs_state* s, float sep, cs_stream stream);
 CS_API int cs_sim_final_check(const cs_state* s, cs_stream stream);
 
 /*
+ * Recompute the arg-max key of the NEXT pick (and, for world_size > 1, the candidate pack) from
+ * the current h without touching h, voronoi or n_sel.  Call it after h was changed outside
+ * cs_fps_step (roll-back to a snapshot, a reconstructed bisect state) and for "global max h"
+ * queries.  Replaces the stand-alone uses of argmax_cuda (kernels/argmax.cu:179-193) in
+ * cuda/multi/sharded.py:112-131, 470-490 and kernels/simulate.cu:84, multi.cu:511-517.
+ */
+CS_API int cs_scan_argmax(const cs_state* s, cs_stream stream);
+
+/*
  * Several probes at once: `n_lanes` (1..8) independent states that share X / norms /
  * N_local / D / shard_offset / world_size but own their h, voronoi, centres and control
  * block.  One pass over X serves every lane; each lane's arithmetic is that of cs_fps_step.

@@ -189,6 +189,17 @@ class FakeNative:
         self._publish(s, a, k)
         ctl.n_sel = i + 1
 
+    def scan_argmax(self, s, stream):
+        a = self._arrays(s)
+        ctl = self._ctl(s)
+        if s.N_local > 0:
+            val, li = oracle.argmax(a["h"])
+            k = make_key(val, li + s.shard_offset) if li >= 0 else 0
+        else:
+            k = 0
+        ctl.key[ctl.n_sel & 1] = k
+        self._publish(s, a, k)
+
     def sim_begin(self, s, sep, stream):
         ctl = self._ctl(s)
         ctl.viable = 0

@@ -1,0 +1,57 @@
+"""Worker of the multi-GPU test (one process per GPU, NCCL).  Run by tests/test_gpu_multi.py."""
+from __future__ import annotations
+
+import json
+import os
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+
+def main() -> None:
+    cfg = json.loads(sys.argv[1])
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import oracle
+    from coresets_b200 import engine, fps_cuda, fps_sharded
+    from tests.data import gaussian_mixture, with_duplicates
+
+    failures = []
+    for case in cfg["cases"]:
+        N, D, k, seed = case["N"], case["D"], case["k"], case.get("seed")
+        X_np = with_duplicates(gaussian_mixture(N, D, 8, seed=N + D), 30, seed=2)
+        sizes = case["sizes"]
+        offs = [sum(sizes[:r]) for r in range(world)]
+        X_local = torch.from_numpy(np.ascontiguousarray(X_np[offs[rank] : offs[rank] + sizes[rank]])).to(dev)
+        sel, eps = fps_sharded(X_local, k, seed=seed, verbose=False)
+        # norms exactly as every rank computed them for its own shard
+        norms = np.concatenate([
+            engine.row_norms(torch.from_numpy(np.ascontiguousarray(X_np[offs[r] : offs[r] + sizes[r]])).to(dev)).cpu().numpy()
+            if sizes[r] > 0 else np.zeros(0, np.float32) for r in range(world)])
+        o_sel, o_eps, _, _ = oracle.fps_sharded(X_np, norms, k, sizes, first=seed or 0)
+        if not np.array_equal(sel.cpu().numpy(), o_sel):
+            failures.append(f"{case}: selected differs from the oracle on rank {rank}")
+        if not np.array_equal(eps.numpy().view(np.int32), o_eps.view(np.int32)):
+            failures.append(f"{case}: epsilons differ on rank {rank}")
+        if rank == 0 and max(sizes) == N:   # rank 0 holds everything: compare with single-GPU fps_cuda too
+            one = fps_cuda(X_local, k, seed=None if seed is None else torch.tensor([seed]))
+            if not torch.equal(one, sel):
+                failures.append(f"{case}: fps_sharded != fps_cuda")
+        dist.barrier()
+    out = Path(cfg["out_dir"]) / f"result_{rank}.json"
+    out.write_text(json.dumps({"failures": failures}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,70 @@
+"""fps_sharded over real NCCL ranks (one process per GPU) against the oracle's emulation of the
+reference's sharded driver.  With one visible GPU only the world_size = 1 group is exercised."""
+import json
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _launch(world: int, cfg: dict, timeout: int = 600) -> None:
+    port = _free_port()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r),
+                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(ROOT / "tests" / "nccl_worker.py"), json.dumps(cfg)],
+                                      env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = []
+    try:
+        for p in procs:
+            o, _ = p.communicate(timeout=timeout)
+            outs.append(o)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+    for r, p in enumerate(procs):
+        assert p.returncode == 0, f"rank {r} failed:\n{outs[r][-3000:]}"
+    for r in range(world):
+        res = json.loads((Path(cfg["out_dir"]) / f"result_{r}.json").read_text())
+        assert res["failures"] == [], res["failures"]
+
+
+def _cases(world: int):
+    def split(N, uneven=False, empty=False):
+        base = N // world
+        sizes = [base] * (world - 1) + [N - base * (world - 1)]
+        if empty and world > 1:
+            sizes = [0] + [N // (world - 1)] * (world - 2) + [N - (N // (world - 1)) * (world - 2)]
+        return sizes
+    return [
+        dict(N=16383, D=128, k=300, sizes=split(16383)),           # uneven shards (remainder on the last rank)
+        dict(N=6000, D=64, k=200, sizes=split(6000), seed=4321),   # seeded first pick
+        dict(N=5001, D=256, k=96, sizes=split(5001, empty=True)),  # an empty shard when world > 1
+        dict(N=3000, D=50, k=64, sizes=split(3000)),               # D % 4 != 0
+    ]
+
+
+def test_fps_sharded_nccl_world1(tmp_path):
+    _launch(1, dict(cases=_cases(1), out_dir=str(tmp_path)))
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fps_sharded_nccl_multi(tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _launch(world, dict(cases=_cases(world), out_dir=str(tmp_path)))
