@@ -5,12 +5,14 @@ reference package (src/coresets/__init__.py:1-20): ``fps_cuda``, ``fps_sharded``
 """
 from . import io
 from ._version import __version__
-from .cuda import warmup_fast_fps
+from .cuda import accrete, warmup_fast_fps
 from .cuda.fps import fps as fps_cuda
-from .cuda.multi import compute_shard_layout, fps_sharded
+from .cuda.multi import accrete_sharded, compute_shard_layout, fps_sharded
 from .io import load_result, save_result
 
 __all__ = [
+    "accrete",
+    "accrete_sharded",
     "fps_cuda",
     "fps_sharded",
     "compute_shard_layout",

@@ -1,4 +1,5 @@
 from . import multi
+from .accrete import accrete
 from .fps import fps
 from .._native import ensure_compiled
 
@@ -9,4 +10,4 @@ def warmup_fast_fps() -> None:
     ensure_compiled()
 
 
-__all__ = ["fps", "warmup_fast_fps", "multi"]
+__all__ = ["accrete", "fps", "warmup_fast_fps", "multi"]

@@ -1,4 +1,6 @@
 from .fps_sharded import fps_sharded
 from .layout import ShardLayout, compute_shard_layout
+from .sharded import accrete_sharded, accrete_voronoi_multi_sharded
 
-__all__ = ["fps_sharded", "compute_shard_layout", "ShardLayout"]
+__all__ = ["fps_sharded", "compute_shard_layout", "ShardLayout", "accrete_sharded",
+           "accrete_voronoi_multi_sharded"]

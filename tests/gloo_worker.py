@@ -25,6 +25,8 @@ def main() -> None:
     sharded_mod = importlib.import_module("coresets_b200.cuda.multi.fps_sharded")
     sharded_mod._REQUIRE_CUDA = False
 
+    if cfg.get("mode") == "accrete":
+        return accrete_mode(cfg, rank, world)
     X = np.load(cfg["x_path"])
     sizes = cfg["sizes"]
     off = sum(sizes[:rank])
@@ -47,6 +49,36 @@ def main() -> None:
         assert sel.dtype == torch.int64 and eps.dtype == torch.float32 and eps.device.type == "cpu"
         np.save(out / f"sel_{rank}.npy", sel.numpy())
         np.save(out / f"eps_{rank}.npy", eps.numpy())
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def accrete_mode(cfg, rank, world) -> None:
+    """accrete_voronoi_multi_sharded over gloo ranks for the cases of a golden file."""
+    sh = importlib.import_module("coresets_b200.cuda.multi.sharded")
+    sh._REQUIRE_CUDA = False
+    from coresets_b200.cuda.multi.layout import compute_shard_layout
+    out = Path(cfg["out_dir"])
+    try:
+        for case in cfg["cases"]:
+            for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK"):
+                os.environ.pop(k, None)
+            os.environ.update(case.get("env", {}))
+            X = np.load(case["x_path"])
+            order = np.load(case["order_path"])
+            sizes, offs = compute_shard_layout(X.shape[0], world)
+            Xl = torch.from_numpy(np.ascontiguousarray(X[offs[rank] : offs[rank] + sizes[rank]]))
+            kw = {}
+            if case.get("checkpoint"):
+                kw.update(checkpoint_path=str(out / case["checkpoint"]), checkpoint_every=case.get("checkpoint_every", 0))
+            if case.get("resume"):
+                kw.update(resume_from=str(out / case["resume"]))
+            res = sh.accrete_voronoi_multi_sharded(
+                Xl, rank, world, case["n_anchor"], X.shape[0], sizes, torch.from_numpy(order),
+                max_k=case["max_k"], n_target=case.get("n_target"), verbose=False, **kw)
+            assert res.dtype == torch.int64
+            np.save(out / f"{case['name']}_{rank}.npy", res.numpy())
     finally:
         dist.barrier()
         dist.destroy_process_group()

@@ -1,0 +1,75 @@
+"""Accretion host logic on CPU against golden vectors written by the REFERENCE's own drivers
+(tests/golden/make_golden_accrete_cpu.py runs src/coresets/cuda/accrete.py and
+src/coresets/cuda/multi/sharded.py on CPU tensors with the oracle as their kernel extension).
+Here the package's drivers run on the oracle-backed stand-in native library; index lists and the
+per-commit trace (values and separations bit for bit) must be identical."""
+import importlib
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from coresets_b200 import _native
+from tests.fake_native import FakeNative
+from tests.golden.make_golden_accrete_cpu import CASES, PHASES, make_case, read_trace
+from tests.test_sharded_gloo import _run
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+acc_mod = importlib.import_module("coresets_b200.cuda.accrete")
+
+
+@pytest.fixture()
+def fake_native(monkeypatch):
+    monkeypatch.setattr(_native, "_native", FakeNative())
+    monkeypatch.setattr(acc_mod, "_REQUIRE_CUDA", False)
+    for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK"):
+        monkeypatch.delenv(k, raising=False)
+    yield
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if "n_target" not in c])
+def test_single_gpu_driver_matches_reference(fake_native, name, tmp_path):
+    c = CASES[name]
+    z = np.load(GOLDEN / f"accrete_cpu_{name}.npz")
+    X, order = make_case(c)
+    np.testing.assert_array_equal(order, z["anchor_order"])
+    Xt = torch.from_numpy(X)
+    tr = str(tmp_path / "trace.tsv")
+    got = acc_mod.accrete(Xt[: c["n_anchor"]], Xt[c["n_anchor"] :], torch.from_numpy(order), c["max_k"],
+                          verbose=False, trace_path=tr)
+    np.testing.assert_array_equal(got.numpy(), z["single"])
+    mine = read_trace(tr)
+    for key in ("trace_phase", "trace_pos", "trace_idx"):
+        np.testing.assert_array_equal(mine[key], z[key])
+    # values and running separations: every bit (hex floats in the trace)
+    np.testing.assert_array_equal(mine["trace_val"].view(np.int64), z["trace_val"].view(np.int64))
+    np.testing.assert_array_equal(mine["trace_sep"].view(np.int64), z["trace_sep"].view(np.int64))
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_sharded_driver_matches_reference(tmp_path, world):
+    cases = []
+    for name, c in CASES.items():
+        X, order = make_case(c)
+        np.save(tmp_path / f"{name}_x.npy", X)
+        np.save(tmp_path / f"{name}_o.npy", order)
+        base = dict(x_path=str(tmp_path / f"{name}_x.npy"), order_path=str(tmp_path / f"{name}_o.npy"),
+                    n_anchor=c["n_anchor"], max_k=c["max_k"], n_target=c.get("n_target"))
+        cases.append(dict(base, name=f"{name}_plain"))
+        cases.append(dict(base, name=f"{name}_knobs", env={"CORESETS_BISECT_SEED": "1", "CORESETS_FILL_CHUNK": "256"}))
+    _run(world, dict(mode="accrete", cases=cases, out_dir=str(tmp_path)), timeout=900)
+    for name in CASES:
+        z = np.load(GOLDEN / f"accrete_cpu_{name}.npz")
+        for r in range(world):
+            np.testing.assert_array_equal(np.load(tmp_path / f"{name}_plain_{r}.npy"), z[f"sharded_w{world}"])
+            np.testing.assert_array_equal(np.load(tmp_path / f"{name}_knobs_{r}.npy"), z[f"sharded_w{world}_knobs"])
+
+
+def test_accrete_validation(fake_native):
+    X = torch.zeros(8, 4)
+    with pytest.raises(ValueError, match="empty"):
+        acc_mod.accrete(X[:0], X, torch.arange(0), 2, verbose=False)
+    with pytest.raises(ValueError, match="mismatch"):
+        acc_mod.accrete(X, torch.zeros(8, 5), torch.arange(8), 2, verbose=False)
