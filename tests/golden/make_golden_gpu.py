@@ -151,6 +151,66 @@ def midsize_compare(coresets, dev, out):
     (out / "midsize_compare.json").write_text(json.dumps(results, indent=1))
 
 
+ACCRETE_CASES = {
+    # the reference's own determinism configs (tests/slurm/test_determinism.sh:43-46), scaled K
+    "acc_8192x32_k2048": dict(gen="jitter", N=8192, D=32, max_k=11, n_anchor=4096, order="arange"),
+    "acc_16383x128_k1024": dict(gen="jitter", N=16383, D=128, max_k=10, n_anchor=8191, order="arange"),
+    "acc_mix_20000x64_k512_fps": dict(gen="mix", N=20000, D=64, max_k=9, n_anchor=8000, order="fps"),
+}
+
+
+def accrete_goldens(coresets, dev, out, compare):
+    """Reference `accrete` and one-rank `accrete_sharded` (default knobs and
+    CORESETS_BISECT_SEED=1 CORESETS_FILL_CHUNK=256) on the GPU; index lists + the single-GPU trace."""
+    from tests.golden.make_golden_accrete_cpu import read_trace
+    from tests.data import clustered_jitter, gaussian_mixture
+    import time
+    for name, c in ACCRETE_CASES.items():
+        X_np = clustered_jitter(c["N"], c["D"], seed=42) if c["gen"] == "jitter" else gaussian_mixture(c["N"], c["D"], 12, seed=c["N"])
+        X = torch.from_numpy(X_np).to(dev)
+        na = c["n_anchor"]
+        if c["order"] == "arange":
+            order = torch.arange(na, dtype=torch.long, device=dev)
+        else:
+            order = coresets.fps_cuda(X[:na].contiguous(), na)
+        tr = str(out / f"{name}.tsv")
+        t0 = time.time()
+        single = coresets.accrete(X[:na], X[na:], order, c["max_k"], verbose=False, trace_path=tr)
+        torch.cuda.synchronize()
+        t_single = time.time() - t0
+        rec = dict(anchor_order=order.cpu().numpy(), single=single.cpu().numpy().astype(np.int64), **read_trace(tr))
+        times = {"reference_accrete_s": t_single}
+        for tag, env in (("plain", {}), ("knobs", {"CORESETS_BISECT_SEED": "1", "CORESETS_FILL_CHUNK": "256"})):
+            for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK"):
+                os.environ.pop(k, None)
+            os.environ.update(env)
+            t0 = time.time()
+            res = coresets.accrete_sharded(X, order, na, max_k=c["max_k"], verbose=False)
+            torch.cuda.synchronize()
+            times[f"reference_accrete_sharded_{tag}_s"] = time.time() - t0
+            rec[f"sharded_{tag}"] = res.cpu().numpy().astype(np.int64)
+        for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK"):
+            os.environ.pop(k, None)
+        np.savez_compressed(out / f"{name}.npz", **rec)
+        msg = {k_: bool(np.array_equal(rec["single"], rec[k_])) for k_ in ("sharded_plain", "sharded_knobs")}
+        print(f"[golden] {name}: {len(rec['single'])} ids; reference variants equal to single: {msg}; {times}", flush=True)
+        if compare:
+            import coresets_b200
+            t0 = time.time()
+            mine = coresets_b200.accrete(X[:na], X[na:], order, c["max_k"], verbose=False)
+            torch.cuda.synchronize()
+            t_mine = time.time() - t0
+            ms = coresets_b200.accrete_sharded(X, order, na, max_k=c["max_k"], verbose=False)
+            os.environ.update({"CORESETS_BISECT_SEED": "1", "CORESETS_FILL_CHUNK": "256"})
+            mk = coresets_b200.accrete_sharded(X, order, na, max_k=c["max_k"], verbose=False)
+            for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK"):
+                os.environ.pop(k, None)
+            print(f"[compare] {name}: accrete={bool(np.array_equal(mine.cpu().numpy(), rec['single']))} "
+                  f"sharded={bool(np.array_equal(ms.cpu().numpy(), rec['sharded_plain']))} "
+                  f"sharded_knobs={bool(np.array_equal(mk.cpu().numpy(), rec['sharded_knobs']))} "
+                  f"engine_accrete_s={t_mine:.2f} reference_accrete_s={t_single:.2f}", flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=str(ROOT / "gpurun_out" / "golden"))
@@ -184,6 +244,7 @@ def main() -> None:
         print(f"[golden] {name}: K={K} first={sel_api[:5].tolist()} last={sel_api[-3:].tolist()}", flush=True)
         if a.compare:
             compare_with_engine(name, X, K, seeds, sel_api, eps, h, v)
+    accrete_goldens(coresets, dev, out, a.compare)
     if a.compare:
         midsize_compare(coresets, dev, out)
     dist.destroy_process_group()

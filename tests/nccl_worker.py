@@ -26,6 +26,9 @@ def main() -> None:
     from tests.data import gaussian_mixture, with_duplicates
 
     failures = []
+    if cfg.get("mode") == "accrete":
+        failures = accrete_mode(cfg, rank, world, dev)
+        cfg = dict(cfg, cases=[])
     for case in cfg["cases"]:
         N, D, k, seed = case["N"], case["D"], case["k"], case.get("seed")
         X_np = with_duplicates(gaussian_mixture(N, D, 8, seed=N + D), 30, seed=2)
@@ -51,6 +54,34 @@ def main() -> None:
     out.write_text(json.dumps({"failures": failures}))
     dist.barrier()
     dist.destroy_process_group()
+
+
+def accrete_mode(cfg, rank, world, dev):
+    """accrete_sharded over NCCL ranks against the golden lists written by the reference on a B200."""
+    import coresets_b200
+    from coresets_b200.cuda.multi.layout import compute_shard_layout
+    from tests.data import clustered_jitter, gaussian_mixture
+    from tests.golden.make_golden_gpu import ACCRETE_CASES
+    golden = ROOT / "tests" / "golden"
+    failures = []
+    for name, c in ACCRETE_CASES.items():
+        z = np.load(golden / f"{name}.npz")
+        X_np = clustered_jitter(c["N"], c["D"], seed=42) if c["gen"] == "jitter" else gaussian_mixture(c["N"], c["D"], 12, seed=c["N"])
+        sizes, offs = compute_shard_layout(c["N"], world)
+        Xl = torch.from_numpy(np.ascontiguousarray(X_np[offs[rank] : offs[rank] + sizes[rank]])).to(dev)
+        order = torch.from_numpy(z["anchor_order"]).to(dev)
+        for tag, env in (("plain", {}), ("knobs", {"CORESETS_BISECT_SEED": "1", "CORESETS_FILL_CHUNK": "256"})):
+            for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK"):
+                os.environ.pop(k, None)
+            os.environ.update(env)
+            res = coresets_b200.accrete_sharded(Xl, order, c["n_anchor"], max_k=c["max_k"], verbose=False)
+            if not np.array_equal(res.cpu().numpy(), z[f"sharded_{tag}"]):
+                nd = int((res.cpu().numpy() != z[f"sharded_{tag}"]).sum())
+                failures.append(f"{name}/{tag}: {nd} ids differ from the reference on rank {rank} (world {world})")
+        for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK"):
+            os.environ.pop(k, None)
+        dist.barrier()
+    return failures
 
 
 if __name__ == "__main__":

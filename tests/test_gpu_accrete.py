@@ -1,0 +1,52 @@
+"""Accretion on the GPU against golden lists written by the reference's own CUDA `accrete` /
+`accrete_sharded` on a B200 (tests/golden/make_golden_gpu.py), including the per-commit trace."""
+import importlib
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def _cases():
+    from tests.golden.make_golden_gpu import ACCRETE_CASES
+    return {n: c for n, c in ACCRETE_CASES.items() if (GOLDEN / f"{n}.npz").is_file()}
+
+
+def test_accrete_golden_files_present():
+    assert len(_cases()) >= 3
+
+
+@pytest.mark.parametrize("name", ["acc_8192x32_k2048", "acc_16383x128_k1024", "acc_mix_20000x64_k512_fps"])
+def test_accrete_matches_reference(name, tmp_path):
+    import coresets_b200
+    from tests.data import clustered_jitter, gaussian_mixture
+    from tests.golden.make_golden_accrete_cpu import read_trace
+    c = _cases()[name]
+    z = np.load(GOLDEN / f"{name}.npz")
+    X_np = clustered_jitter(c["N"], c["D"], seed=42) if c["gen"] == "jitter" else gaussian_mixture(c["N"], c["D"], 12, seed=c["N"])
+    X = torch.from_numpy(X_np).cuda()
+    na = c["n_anchor"]
+    order = torch.from_numpy(z["anchor_order"]).cuda()
+    if c["order"] == "fps":   # the anchor ordering itself is the reference's fps_cuda output
+        np.testing.assert_array_equal(coresets_b200.fps_cuda(X[:na].contiguous(), na).cpu().numpy(), z["anchor_order"])
+    tr = str(tmp_path / "t.tsv")
+    got = coresets_b200.accrete(X[:na], X[na:], order, c["max_k"], verbose=False, trace_path=tr)
+    assert got.is_cuda and got.dtype == torch.int64
+    np.testing.assert_array_equal(got.cpu().numpy(), z["single"])
+    mine = read_trace(tr)
+    for key in ("trace_phase", "trace_pos", "trace_idx"):
+        np.testing.assert_array_equal(mine[key], z[key])
+    np.testing.assert_array_equal(mine["trace_val"].view(np.int64), z["trace_val"].view(np.int64))
+    np.testing.assert_array_equal(mine["trace_sep"].view(np.int64), z["trace_sep"].view(np.int64))
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_accrete_sharded_matches_reference(tmp_path, world):
+    from tests.test_gpu_multi import _launch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _launch(world, dict(mode="accrete", cases=[], out_dir=str(tmp_path)), timeout=1500)
