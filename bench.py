@@ -329,25 +329,18 @@ def run_ours(args):
 
 
 class HostMatrix:
-    """Host-side copy of a rank's rows.  Fully page-locked when the machine allows it; otherwise
-    ordinary pageable memory that is moved through a ring of two page-locked staging buffers
-    (CPU copy of chunk i+1 overlaps the DMA of chunk i), the way a user's large numpy array
-    reaches the device."""
+    """Host-side copy of a rank's rows in ordinary (pageable) memory, moved to and from the device
+    through a ring of two page-locked 1 GiB staging buffers: the CPU copy of chunk i+1 overlaps the
+    DMA of chunk i.  This is how a user's large numpy array reaches the device; page-locking the
+    whole matrix is not attempted (153.6 GB of locked pages starve a 196 GB host)."""
     RING_BYTES = 1 << 30
 
     def __init__(self, X: torch.Tensor):
         self.shape, self.dtype = tuple(X.shape), X.dtype
-        self.pinned = True
-        try:
-            self.host = torch.empty(self.shape, dtype=self.dtype, pin_memory=True)
-        except Exception:
-            self.pinned = False
-            torch.cuda.synchronize(X.device)
-            self.host = torch.empty(self.shape, dtype=self.dtype)
-        self.ring = None
-        if not self.pinned:
-            rows = max(1, self.RING_BYTES // max(1, self.shape[1] * 4))
-            self.ring = [torch.empty((rows, self.shape[1]), dtype=self.dtype, pin_memory=True) for _ in range(2)]
+        self.pinned = False
+        self.host = torch.empty(self.shape, dtype=self.dtype)
+        rows = max(1, self.RING_BYTES // max(1, self.shape[1] * 4))
+        self.ring = [torch.empty((rows, self.shape[1]), dtype=self.dtype, pin_memory=True) for _ in range(2)]
         self._move(X, to_device=False)
 
     def _move(self, X: torch.Tensor, to_device: bool) -> None:
@@ -388,6 +381,21 @@ class HostMatrix:
         self._move(X, to_device=True)
 
 
+def host_memory_available() -> int:
+    """Bytes this process group may still use: the smaller of the machine's available memory and the
+    head-room under the cgroup limit (a container can be capped far below the machine)."""
+    import psutil
+    avail = psutil.virtual_memory().available
+    try:
+        limit = Path("/sys/fs/cgroup/memory.max").read_text().strip()
+        used = int(Path("/sys/fs/cgroup/memory.current").read_text().strip())
+        if limit != "max":
+            avail = min(avail, int(limit) - used)
+    except Exception:
+        pass
+    return int(avail)
+
+
 def run_e2e(args, X, w, world, rank, device, K, W, off):
     """One complete job through the engine from HOST rows: H2D of the rank's rows -> norms -> first
     pick -> K picks -> D2H of (selected, epsilons).  The W warm-up picks between the load phase and
@@ -397,9 +405,10 @@ def run_e2e(args, X, w, world, rank, device, K, W, off):
     import psutil
     n_local, dim = X.shape
     nbytes = n_local * dim * 4
-    avail = psutil.virtual_memory().available
+    avail = host_memory_available()
     share = max(1, min(world, torch.cuda.device_count()))
-    ok = torch.tensor([1 if nbytes + (16 << 30) / share < avail / share else 0], device=device)
+    # all ranks of this node together must leave a fifth of the host memory (and 24 GiB) free
+    ok = torch.tensor([1 if (nbytes + (4 << 30)) * share + (24 << 30) < 0.8 * avail else 0], device=device)
     if world > 1:
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if int(ok.item()) == 0:

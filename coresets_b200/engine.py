@@ -186,9 +186,13 @@ class ShardEngine:
         key = (n, rules, self.mode)
         g = self._graphs.get(key)
         if g is None:
+            # Nothing may be in flight while the stream captures: with collectives in the body the
+            # process group's watchdog thread polls the events of earlier eager collectives, and
+            # an event query from another thread invalidates a capture in the default "global"
+            # error mode.  Drain the device first and confine capture errors to this thread.
+            torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
-            # side-stream warm-up is not needed: every kernel has run eagerly (the first pick)
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
                 for _ in range(n):
                     self._pick_body(rules)
             self._graphs[key] = g

@@ -1,9 +1,11 @@
 """Worker of the multi-GPU test (one process per GPU, NCCL).  Run by tests/test_gpu_multi.py."""
 from __future__ import annotations
 
+import datetime
 import json
 import os
 import sys
+import traceback
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent.parent
@@ -20,7 +22,8 @@ def main() -> None:
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=int(cfg.get("pg_timeout", 150))))
     import oracle
     from coresets_b200 import engine, fps_cuda, fps_sharded
     from tests.data import gaussian_mixture, with_duplicates
@@ -85,4 +88,10 @@ def accrete_mode(cfg, rank, world, dev):
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:  # a rank that dies must not leave its peers waiting in a collective
+        traceback.print_exc()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(1)

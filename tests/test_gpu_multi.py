@@ -2,6 +2,7 @@
 reference's sharded driver.  With one visible GPU only the world_size = 1 group is exercised."""
 import json
 import os
+import time
 import socket
 import subprocess
 import sys
@@ -20,7 +21,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _launch(world: int, cfg: dict, timeout: int = 600) -> None:
+def _launch(world: int, cfg: dict, timeout: int = 420) -> None:
     port = _free_port()
     procs = []
     for r in range(world):
@@ -29,14 +30,15 @@ def _launch(world: int, cfg: dict, timeout: int = 600) -> None:
         procs.append(subprocess.Popen([sys.executable, str(ROOT / "tests" / "nccl_worker.py"), json.dumps(cfg)],
                                       env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     outs = []
-    try:
-        for p in procs:
-            o, _ = p.communicate(timeout=timeout)
-            outs.append(o)
-    finally:
-        for p in procs:
-            if p.poll() is None:
-                p.kill()
+    deadline = time.time() + timeout
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=max(1.0, deadline - time.time()))
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+            o = (o or "") + "\n[killed after timeout]"
+        outs.append(o)
     for r, p in enumerate(procs):
         assert p.returncode == 0, f"rank {r} failed:\n{outs[r][-3000:]}"
     for r in range(world):
