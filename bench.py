@@ -414,6 +414,8 @@ def run_e2e(args, X, w, world, rank, device, K, W, off):
     if int(ok.item()) == 0:
         return {"value": None, "unit": UNIT, "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
                 "skipped": f"host memory: {nbytes/1e9:.1f} GB per rank needed, {avail/1e9:.1f} GB available"}
+    # torchrun pins OMP_NUM_THREADS=1; the pageable -> page-locked copies want this rank's share of the cores
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) // share))
     hm = HostMatrix(X)
     torch.cuda.synchronize(device)
     sel_host = torch.empty(1 + W + K, dtype=torch.int64, pin_memory=True)

@@ -48,7 +48,7 @@ def main() -> None:
             failures.append(f"{case}: selected differs from the oracle on rank {rank}")
         if not np.array_equal(eps.numpy().view(np.int32), o_eps.view(np.int32)):
             failures.append(f"{case}: epsilons differ on rank {rank}")
-        if rank == 0 and max(sizes) == N:   # rank 0 holds everything: compare with single-GPU fps_cuda too
+        if sizes[rank] == N:                # this rank holds everything: compare with single-GPU fps_cuda too
             one = fps_cuda(X_local, k, seed=None if seed is None else torch.tensor([seed]))
             if not torch.equal(one, sel):
                 failures.append(f"{case}: fps_sharded != fps_cuda")
