@@ -13,7 +13,7 @@ from typing import Optional
 
 from . import build as _build
 
-CS_ABI_VERSION = 1
+CS_ABI_VERSION = 2
 CS_CTL_BYTES = 256
 
 MODE_PRUNE = 0
@@ -21,11 +21,14 @@ MODE_DENSE = 1
 RULE_NONE = 0
 RULE_SIM_SINGLE = 1
 RULE_SIM_SHARDED = 2
+XCHG_GATHER = 0
+XCHG_PEER = 1
+MAX_PEERS = 8
 
 EXPORTS = (
     "cs_version", "cs_error_string", "cs_last_cuda_error", "cs_device_check", "cs_init_state",
     "cs_reset_ctl", "cs_force_pick", "cs_commit_bound", "cs_fps_step", "cs_sim_begin",
-    "cs_sim_final_check", "cs_scan_argmax", "cs_fps_step_lanes", "cs_fps_step_noalloc",
+    "cs_sim_final_check", "cs_xchg_window_words", "cs_xchg_wait", "cs_scan_argmax", "cs_fps_step_lanes", "cs_fps_step_noalloc",
 )
 
 
@@ -49,6 +52,11 @@ class CsState(ctypes.Structure):
         ("ctl", ctypes.c_void_p),
         ("pack_local", ctypes.c_void_p),
         ("pack_all", ctypes.c_void_p),
+        ("rank", ctypes.c_int32),
+        ("xchg", ctypes.c_int32),
+        ("peer_win", ctypes.c_void_p * MAX_PEERS),
+        ("xchg_timeout_ms", ctypes.c_int32),
+        ("reserved0", ctypes.c_int32),
     ]
 
 
@@ -65,7 +73,8 @@ class CtlView(ctypes.Structure):
         ("live_rows", ctypes.c_uint64),
         ("last_val", ctypes.c_float),
         ("last_idx", ctypes.c_int32),
-        ("reserved", ctypes.c_uint8 * (CS_CTL_BYTES - 56)),
+        ("xseq", ctypes.c_uint32),
+        ("reserved", ctypes.c_uint8 * (CS_CTL_BYTES - 60)),
     ]
 
 
@@ -108,11 +117,14 @@ class Native:
             ("cs_sim_begin", [sp, ctypes.c_float, vp]),
             ("cs_sim_final_check", [sp, vp]),
             ("cs_scan_argmax", [sp, vp]),
+            ("cs_xchg_wait", [sp, vp]),
             ("cs_fps_step_lanes", [sp, ctypes.c_int32, ctypes.c_uint32, vp]),
         ):
             fn = getattr(L, name)
             fn.restype = ctypes.c_int
             fn.argtypes = args
+        L.cs_xchg_window_words.restype = ctypes.c_int64
+        L.cs_xchg_window_words.argtypes = [ctypes.c_int32, ctypes.c_int32]
         L.cs_fps_step_noalloc.restype = ctypes.c_int
         L.cs_fps_step_noalloc.argtypes = [vp, vp, vp, vp, ctypes.c_int64, ctypes.c_int32, ctypes.c_int64, vp,
                                           ctypes.c_float, vp, ctypes.c_int32, ctypes.c_uint32, vp, vp, vp]
@@ -152,6 +164,15 @@ class Native:
 
     def sim_final_check(self, s: CsState, stream: int) -> None:
         self._check(self.lib.cs_sim_final_check(ctypes.byref(s), stream), "cs_sim_final_check")
+
+    def xchg_window_words(self, world_size: int, D: int) -> int:
+        n = int(self.lib.cs_xchg_window_words(world_size, D))
+        if n < 0:
+            self._check(n, "cs_xchg_window_words")
+        return n
+
+    def xchg_wait(self, s: CsState, stream: int) -> None:
+        self._check(self.lib.cs_xchg_wait(ctypes.byref(s), stream), "cs_xchg_wait")
 
     def scan_argmax(self, s: CsState, stream: int) -> None:
         self._check(self.lib.cs_scan_argmax(ctypes.byref(s), stream), "cs_scan_argmax")

@@ -11,6 +11,7 @@
 #include "coresets_b200.h"
 
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdint.h>
 
 namespace {
@@ -29,11 +30,12 @@ struct Ctl {
     u64 live_rows;
     float last_val;
     int last_idx;
+    unsigned xseq;      // peer exchange: sequence number of this rank's last published candidate
 };
 static_assert(sizeof(Ctl) <= CS_CTL_BYTES, "control block too large");
 static_assert(sizeof(cs_ctl_view) == CS_CTL_BYTES, "cs_ctl_view must span the control block");
 
-enum { ST_CAPACITY = 1, ST_FORCE_NOT_OWNED = 2 };
+enum { ST_CAPACITY = 1, ST_FORCE_NOT_OWNED = 2, ST_XCHG_TIMEOUT = 3 };
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
@@ -121,13 +123,103 @@ __device__ __forceinline__ float warp_dot_generic(const float* __restrict__ row,
     return warp_tree_sum(acc);
 }
 
+// ---- candidate exchange ---------------------------------------------------------------------
+// xchg == CS_XCHG_GATHER: the candidate goes to pack_local and the caller all-gathers it.
+// xchg == CS_XCHG_PEER:   the publishing block stores the candidate straight into every rank's
+// exchange window over NVLink (plain peer stores) and then raises a per-rank flag with the
+// sequence number; consumers spin on the flags in their OWN memory.  Window layout (32-bit words):
+//   flags [2][W] padded to 64 words, then packs [2][W][stride], stride = 4 + D rounded up to 4.
+// Parity = sequence number & 1.  A rank publishes sequence s+1 only after it consumed s, which
+// needed every peer's s, which they published after consuming s-1: two buffers are enough.
+__device__ __forceinline__ int xchg_stride(int D) { return (4 + D + 3) & ~3; }
+constexpr int kFlagWords = 64;
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// All threads of ONE block call this.  k == 0 publishes "nothing"; l is the local row of the key.
+__device__ void publish_candidate(const cs_state& s, Ctl* ctl, const u64 k, const int64_t l) {
+    const int D = s.D;
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(s.X + (k ? l : 0) * (int64_t)D);
+    const uint32_t norm_bits = k ? __float_as_uint(s.norms[l]) : 0u;
+    if (s.xchg == CS_XCHG_GATHER) {
+        uint32_t* p = s.pack_local;
+        if (threadIdx.x == 0) {
+            p[0] = (uint32_t)(k & 0xffffffffu);
+            p[1] = (uint32_t)(k >> 32);
+            p[2] = norm_bits;
+            p[3] = 0u;
+        }
+        for (int c = threadIdx.x; c < D; c += blockDim.x) p[4 + c] = k ? src[c] : 0u;
+        return;
+    }
+    const unsigned seq = ctl->xseq + 1u;
+    const int par = (int)(seq & 1u);
+    const int W = s.world_size, stride = xchg_stride(D);
+    for (int q = 0; q < W; ++q) {
+        uint32_t* p = s.peer_win[q] + kFlagWords + ((int64_t)par * W + s.rank) * stride;
+        if (threadIdx.x == 0) {
+            p[0] = (uint32_t)(k & 0xffffffffu);
+            p[1] = (uint32_t)(k >> 32);
+            p[2] = norm_bits;
+            p[3] = 0u;
+        }
+        for (int c = threadIdx.x; c < D; c += blockDim.x) p[4 + c] = k ? src[c] : 0u;
+    }
+    __threadfence_system();              // every writer orders its stores before the barrier
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int q = 0; q < W; ++q) {
+            volatile uint32_t* f = s.peer_win[q] + par * W + s.rank;
+            *f = seq;
+        }
+        ctl->xseq = seq;
+    }
+}
+
+// Thread 0 of a block waits until every rank's candidate with this rank's current sequence
+// number has landed in the local window; bounded by xchg_timeout_ms, after which the status
+// word records the time-out and the kernel carries on (the host reads the status).
+// Returns the base of the packs to read.
+__device__ const uint32_t* await_candidates(const cs_state& s, Ctl* ctl) {
+    if (s.xchg == CS_XCHG_GATHER || s.world_size <= 1) return s.pack_all;
+    const unsigned seq = ctl->xseq;
+    const int par = (int)(seq & 1u);
+    const int W = s.world_size;
+    uint32_t* win = s.peer_win[s.rank];
+    if (threadIdx.x == 0) {
+        const unsigned long long t0 = global_ns();
+        const unsigned long long limit = (unsigned long long)(s.xchg_timeout_ms > 0 ? s.xchg_timeout_ms : 10000) * 1000000ull;
+        for (int r = 0; r < W; ++r) {
+            volatile uint32_t* f = win + par * W + r;
+            unsigned spins = 0;
+            while (*f != seq) {
+                if ((++spins & 0xffu) == 0 && global_ns() - t0 > limit) {
+                    ctl->status = ST_XCHG_TIMEOUT;
+                    break;
+                }
+            }
+        }
+        __threadfence_system();
+    }
+    __syncthreads();
+    return win + kFlagWords + (int64_t)par * W * xchg_stride(s.D);
+}
+
+__global__ void xchg_wait_kernel(const cs_state s) {
+    (void)await_candidates(s, reinterpret_cast<Ctl*>(s.ctl));
+}
+
 // ---- winner resolution shared by commit_bound and sim_final_check -------------------------
 struct Winner {
     u64 key;
     const float* row;   // D floats (in X or in the gathered packs)
     float norm;
 };
-__device__ __forceinline__ Winner resolve_winner(const cs_state& s, const Ctl* ctl, int i) {
+__device__ __forceinline__ Winner resolve_winner(const cs_state& s, const Ctl* ctl, int i, const uint32_t* packs) {
     Winner w;
     w.row = nullptr;
     w.norm = 0.0f;
@@ -139,16 +231,16 @@ __device__ __forceinline__ Winner resolve_winner(const cs_state& s, const Ctl* c
             w.norm = s.norms[l];
         }
     } else {
-        const int stride = 4 + s.D;
+        const int stride = (s.xchg == CS_XCHG_PEER) ? xchg_stride(s.D) : 4 + s.D;
         w.key = 0;
         int br = -1;
         for (int r = 0; r < s.world_size; ++r) {
-            const uint32_t* p = s.pack_all + (int64_t)r * stride;
+            const uint32_t* p = packs + (int64_t)r * stride;
             u64 k = (u64)p[0] | ((u64)p[1] << 32);
             if (k > w.key) { w.key = k; br = r; }
         }
         if (br >= 0) {
-            const uint32_t* p = s.pack_all + (int64_t)br * stride;
+            const uint32_t* p = packs + (int64_t)br * stride;
             w.norm = __uint_as_float(p[2]);
             w.row = reinterpret_cast<const float*>(p + 4);
         }
@@ -165,7 +257,8 @@ __global__ void __launch_bounds__(kThreads) commit_bound_kernel(const cs_state s
         if (blockIdx.x == 0 && threadIdx.x == 0) ctl->status = ST_CAPACITY;
         return;
     }
-    const Winner w = resolve_winner(s, ctl, i);
+    const uint32_t* packs = await_candidates(s, ctl);
+    const Winner w = resolve_winner(s, ctl, i, packs);
     const float val = key_val(w.key);
     const int64_t gidx = key_idx(w.key);
     const int D = s.D;
@@ -411,18 +504,7 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
     // last block to finish: publish this rank's candidate and advance the pick counter
     __threadfence();
     const u64 k = *reinterpret_cast<volatile u64*>(&ctl->key[slot]);
-    if (s.world_size > 1) {
-        uint32_t* p = s.pack_local;
-        const int64_t l = key_idx(k) - s.shard_offset;
-        if (threadIdx.x == 0) {
-            p[0] = (uint32_t)(k & 0xffffffffu);
-            p[1] = (uint32_t)(k >> 32);
-            p[2] = k ? __float_as_uint(s.norms[l]) : 0u;
-            p[3] = 0u;
-        }
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(s.X + (k ? l : 0) * (int64_t)D);
-        for (int c = threadIdx.x; c < D; c += blockDim.x) p[4 + c] = k ? src[c] : 0u;
-    }
+    if (s.world_size > 1) publish_candidate(s, ctl, k, key_idx(k) - s.shard_offset);
     if (threadIdx.x == 0) {
         ctl->ticket = 0;
         ctl->n_sel = i + 1;
@@ -436,11 +518,14 @@ __global__ void init_state_kernel(float* h, int32_t* v, int64_t N, Ctl* ctl) {
         h[r] = __uint_as_float(0x7f800000u);
         v[r] = 0;
     }
-    if (blockIdx.x == 0 && threadIdx.x < CS_CTL_BYTES / 4) reinterpret_cast<uint32_t*>(ctl)[threadIdx.x] = 0u;
+    // the exchange sequence number outlives a re-initialisation: peers' flags still hold old values
+    if (blockIdx.x == 0 && threadIdx.x < CS_CTL_BYTES / 4 && threadIdx.x != offsetof(Ctl, xseq) / 4)
+        reinterpret_cast<uint32_t*>(ctl)[threadIdx.x] = 0u;
 }
 
 __global__ void reset_ctl_kernel(Ctl* ctl, int n_sel) {
-    if (threadIdx.x < CS_CTL_BYTES / 4) reinterpret_cast<uint32_t*>(ctl)[threadIdx.x] = 0u;
+    if (threadIdx.x < CS_CTL_BYTES / 4 && threadIdx.x != offsetof(Ctl, xseq) / 4)
+        reinterpret_cast<uint32_t*>(ctl)[threadIdx.x] = 0u;
     __syncthreads();
     if (threadIdx.x == 0) ctl->n_sel = n_sel;
 }
@@ -455,17 +540,7 @@ __global__ void force_pick_kernel(const cs_state s, const int64_t gidx, const fl
         ctl->key[i & 1] = k;
         if (s.world_size <= 1 && !owner) ctl->status = ST_FORCE_NOT_OWNED;
     }
-    if (s.world_size > 1) {
-        uint32_t* p = s.pack_local;
-        if (threadIdx.x == 0) {
-            p[0] = (uint32_t)(k & 0xffffffffu);
-            p[1] = (uint32_t)(k >> 32);
-            p[2] = owner ? __float_as_uint(s.norms[l]) : 0u;
-            p[3] = 0u;
-        }
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(s.X + (owner ? l : 0) * (int64_t)s.D);
-        for (int c = threadIdx.x; c < s.D; c += blockDim.x) p[4 + c] = owner ? src[c] : 0u;
-    }
+    if (s.world_size > 1) publish_candidate(s, ctl, k, l);
 }
 
 __global__ void sim_begin_kernel(Ctl* ctl, float sep) {
@@ -476,7 +551,8 @@ __global__ void sim_begin_kernel(Ctl* ctl, float sep) {
 
 __global__ void sim_final_check_kernel(const cs_state s) {
     Ctl* ctl = reinterpret_cast<Ctl*>(s.ctl);
-    const Winner w = resolve_winner(s, ctl, ctl->n_sel);
+    const uint32_t* packs = await_candidates(s, ctl);
+    const Winner w = resolve_winner(s, ctl, ctl->n_sel, packs);
     if (ctl->sep > key_val(w.key)) ctl->viable = 1;   // argmax.cu:152-159, multi.cu:369-384
 }
 
@@ -512,18 +588,7 @@ __global__ void __launch_bounds__(kThreads) scan_argmax_kernel(const cs_state s)
     if (!s_last) return;
     __threadfence();
     const u64 k = *reinterpret_cast<volatile u64*>(&ctl->key[slot]);
-    if (s.world_size > 1) {
-        uint32_t* p = s.pack_local;
-        const int64_t l = key_idx(k) - s.shard_offset;
-        if (threadIdx.x == 0) {
-            p[0] = (uint32_t)(k & 0xffffffffu);
-            p[1] = (uint32_t)(k >> 32);
-            p[2] = k ? __float_as_uint(s.norms[l]) : 0u;
-            p[3] = 0u;
-        }
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(s.X + (k ? l : 0) * (int64_t)s.D);
-        for (int c = threadIdx.x; c < s.D; c += blockDim.x) p[4 + c] = k ? src[c] : 0u;
-    }
+    if (s.world_size > 1) publish_candidate(s, ctl, k, key_idx(k) - s.shard_offset);
     if (threadIdx.x == 0) ctl->ticket = 0;
 }
 
@@ -562,12 +627,19 @@ int validate(const cs_state* s) {
     if (!s || !s->ctl || !s->X_sel || !s->norms_sel || !s->dSL_quarter) return CS_E_ARG;
     if (s->N_local < 0 || s->D <= 0 || s->cap <= 0 || s->world_size < 1 || s->shard_offset < 0) return CS_E_ARG;
     if (s->N_local > 0 && (!s->X || !s->norms || !s->h || !s->voronoi)) return CS_E_ARG;
-    if (s->world_size > 1 && (!s->pack_local || !s->pack_all)) return CS_E_ARG;
+    if (s->xchg != CS_XCHG_GATHER && s->xchg != CS_XCHG_PEER) return CS_E_ARG;
+    if (s->world_size > 1 && s->xchg == CS_XCHG_GATHER && (!s->pack_local || !s->pack_all)) return CS_E_ARG;
+    if (s->world_size > 1 && s->xchg == CS_XCHG_PEER) {
+        if (s->world_size > CS_MAX_PEERS || s->rank < 0 || s->rank >= s->world_size) return CS_E_ARG;
+        for (int r = 0; r < s->world_size; ++r)
+            if (!s->peer_win[r] || ((uintptr_t)s->peer_win[r] & 15u)) return CS_E_ARG;
+    }
     if (s->shard_offset + s->N_local >= (int64_t)1 << 31) return CS_E_RANGE;
     if (s->cap >= (int64_t)1 << 31) return CS_E_RANGE;
     if ((s->D & 3) == 0) {
         if (((uintptr_t)s->X | (uintptr_t)s->X_sel) & 15u) return CS_E_ALIGN;
-        if (s->world_size > 1 && (((uintptr_t)s->pack_local | (uintptr_t)s->pack_all) & 15u)) return CS_E_ALIGN;
+        if (s->world_size > 1 && s->xchg == CS_XCHG_GATHER &&
+            (((uintptr_t)s->pack_local | (uintptr_t)s->pack_all) & 15u)) return CS_E_ALIGN;
     }
     return CS_OK;
 }
@@ -713,6 +785,18 @@ int cs_sim_final_check(const cs_state* s, cs_stream stream) {
     return check_launch();
 }
 
+int64_t cs_xchg_window_words(int32_t world_size, int32_t D) {
+    if (world_size < 1 || D < 1) return CS_E_ARG;
+    return (int64_t)kFlagWords + 2 * (int64_t)world_size * (int64_t)((4 + D + 3) & ~3);
+}
+
+int cs_xchg_wait(const cs_state* s, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    xchg_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(*s);
+    return check_launch();
+}
+
 int cs_scan_argmax(const cs_state* s, cs_stream stream) {
     int rc = validate(s);
     if (rc) return rc;
@@ -836,6 +920,11 @@ extern "C" int cs_fps_step_noalloc(const float* X, const float* norms, float* h,
     s.ctl = scratch;
     s.pack_local = nullptr;
     s.pack_all = nullptr;
+    s.rank = 0;
+    s.xchg = CS_XCHG_GATHER;
+    s.xchg_timeout_ms = 0;
+    s.reserved0 = 0;
+    for (int r = 0; r < CS_MAX_PEERS; ++r) s.peer_win[r] = nullptr;
 
     noalloc_prepare_kernel<<<1, 256, 0, st>>>(scratch, centre, norm_new, D, sel_pos);
     rc = check_launch();

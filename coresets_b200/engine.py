@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist
 
 from . import _native
-from ._native import CsState, CtlView, MODE_DENSE, MODE_PRUNE, RULE_NONE
+from ._native import CsState, CtlView, MODE_DENSE, MODE_PRUNE, RULE_NONE, XCHG_GATHER, XCHG_PEER
 
 _NORM_CHUNK_ELEMS = 1 << 28  # elements of the X*X temporary per chunk (1 GiB of fp32)
 
@@ -48,6 +48,16 @@ def default_mode() -> int:
     if m not in ("prune", "dense"):
         raise ValueError(f"CORESETS_B200_MODE must be 'prune' or 'dense', got {m!r}")
     return MODE_DENSE if m == "dense" else MODE_PRUNE
+
+
+def exchange_mode() -> str:
+    """How candidates travel between ranks: ``nccl`` = one all-gather per pick, ``p2p`` = the step
+    kernel stores its candidate into every peer's symmetric-memory window over NVLink and the next
+    commit kernel waits on flags (no collective launch at all)."""
+    m = os.environ.get("CORESETS_B200_EXCHANGE", "nccl").strip().lower()
+    if m not in ("nccl", "p2p"):
+        raise ValueError(f"CORESETS_B200_EXCHANGE must be 'nccl' or 'p2p', got {m!r}")
+    return m
 
 
 def _graph_picks() -> int:
@@ -95,18 +105,40 @@ class ShardEngine:
         self.selected = torch.empty(self.cap, dtype=i64, device=dev) if record else None
         self.eps = torch.empty(self.cap, dtype=f32, device=dev) if record else None
         self.ctl = torch.zeros(_native.CS_CTL_BYTES // 8, dtype=i64, device=dev)
+        self.pack_local = self.pack_all = self.window = None
+        self.peer_ptrs = []
+        self.rank = 0
+        self.xchg = XCHG_GATHER
+        self._unconsumed = False       # a candidate was published and no commit has consumed it yet
         if self.world_size > 1:
-            self.pack_local = torch.zeros(4 + self.D, dtype=i32, device=dev)
-            self.pack_all = torch.zeros((self.world_size, 4 + self.D), dtype=i32, device=dev)
-        else:
-            self.pack_local = None
-            self.pack_all = None
+            self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+            if self.on_cuda and exchange_mode() == "p2p":
+                self._open_peer_windows()
+            else:
+                self.pack_local = torch.zeros(4 + self.D, dtype=i32, device=dev)
+                self.pack_all = torch.zeros((self.world_size, 4 + self.D), dtype=i32, device=dev)
         self._ctl_host = torch.empty(_native.CS_CTL_BYTES // 8, dtype=i64,
                                      pin_memory=self.on_cuda)
         self._graphs = {}
         self.state = self._make_state()
 
     # -- plumbing ------------------------------------------------------------------------------
+    def _open_peer_windows(self) -> None:
+        """Allocate this rank's exchange window in symmetric memory and map every peer's window
+        (a collective: all ranks construct their engines in the same order)."""
+        import torch.distributed._symmetric_memory as symm_mem
+        if self.world_size > _native.MAX_PEERS:
+            raise ValueError(f"p2p exchange addresses at most {_native.MAX_PEERS} ranks")
+        words = self.native.xchg_window_words(self.world_size, self.D)
+        self.window = symm_mem.empty(words, dtype=torch.int32, device=self.device)
+        self.window.zero_()
+        handle = symm_mem.rendezvous(self.window, self.group if self.group is not None else dist.group.WORLD)
+        self.peer_ptrs = [int(p) for p in handle.buffer_ptrs]
+        self._symm_handle = handle
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)      # every window is zeroed before any peer may store into it
+        self.xchg = XCHG_PEER
+
     def _make_state(self) -> CsState:
         s = CsState()
         s.X = self.X.data_ptr() if self.N_local > 0 else None
@@ -126,6 +158,11 @@ class ShardEngine:
         s.ctl = self.ctl.data_ptr()
         s.pack_local = self.pack_local.data_ptr() if self.pack_local is not None else None
         s.pack_all = self.pack_all.data_ptr() if self.pack_all is not None else None
+        s.rank = self.rank
+        s.xchg = self.xchg
+        for r, ptr in enumerate(self.peer_ptrs):
+            s.peer_win[r] = ptr
+        s.xchg_timeout_ms = int(os.environ.get("CORESETS_B200_XCHG_TIMEOUT_MS", "10000"))
         return s
 
     def rebind(self, *, h: Optional[torch.Tensor] = None, voronoi: Optional[torch.Tensor] = None) -> None:
@@ -148,15 +185,23 @@ class ShardEngine:
     def reset_ctl(self, n_sel: int) -> None:
         self.native.reset_ctl(self.state, int(n_sel), self._stream())
 
+    def _before_publish(self) -> None:
+        # peer exchange: sequence s+1 may only be published once every peer's s has been seen
+        if self.xchg == XCHG_PEER and self._unconsumed:
+            self.native.xchg_wait(self.state, self._stream())
+        self._unconsumed = True
+
     def force_pick(self, global_idx: int, val: float = float("inf")) -> None:
+        self._before_publish()
         self.native.force_pick(self.state, int(global_idx), float(val), self._stream())
 
     def exchange(self) -> None:
-        if self.world_size > 1:
+        if self.world_size > 1 and self.xchg == XCHG_GATHER:
             dist.all_gather_into_tensor(self.pack_all.view(-1), self.pack_local, group=self.group)
 
     def scan(self) -> None:
-        """Recompute the next pick's key (and pack) from the current ``h``."""
+        """Recompute the next pick's key (and candidate) from the current ``h``."""
+        self._before_publish()
         self.native.scan_argmax(self.state, self._stream())
 
     def sim_begin(self, sep: float) -> None:
@@ -164,12 +209,15 @@ class ShardEngine:
 
     def sim_final_check(self) -> None:
         self.native.sim_final_check(self.state, self._stream())
+        self._unconsumed = False
 
     def commit(self, rules: int = RULE_NONE) -> None:
         self.native.commit_bound(self.state, int(rules), self._stream())
+        self._unconsumed = False
 
     def step(self, mode: Optional[int] = None) -> None:
         self.native.fps_step(self.state, self.mode if mode is None else int(mode), self._stream())
+        self._unconsumed = True
 
     # -- picks -------------------------------------------------------------------------------------
     def _pick_body(self, rules: int) -> None:
@@ -223,6 +271,7 @@ class ShardEngine:
                     continue
                 while n >= unit:
                     self._graph(unit, rules).replay()
+                    self._unconsumed = True
                     n -= unit
         for _ in range(n):
             self._pick_body(rules)
@@ -244,6 +293,7 @@ class ShardEngine:
         view = self.read_ctl()
         if view.status != 0:
             what = {1: "more picks were launched than the centre table can hold",
-                    2: "a forced pick named a row this rank does not own"}.get(view.status, "unknown")
+                    2: "a forced pick named a row this rank does not own",
+                    3: "timed out waiting for a peer's candidate (peer exchange)"}.get(view.status, "unknown")
             raise RuntimeError(f"coresets_b200 device status {view.status}: {what}")
         return view

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define CS_ABI_VERSION 1
+#define CS_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define CS_API __attribute__((visibility("default")))
@@ -57,6 +57,12 @@ extern "C" {
 #define CS_RULE_SIM_SINGLE 1u   /* commit_center_with_sep_kernel rules (commit.cu:41-51) */
 #define CS_RULE_SIM_SHARDED 2u  /* reduce_and_commit_multi_sharded_kernel rules (multi.cu:331-340) */
 
+/* how the per-pick candidates travel between ranks (cs_state.xchg) */
+#define CS_XCHG_GATHER 0   /* cs_fps_step writes pack_local; the caller all-gathers into pack_all */
+#define CS_XCHG_PEER 1     /* cs_fps_step stores the candidate into every rank's exchange window
+                              over NVLink and raises a flag; cs_commit_bound waits on the flags   */
+#define CS_MAX_PEERS 8     /* ranks addressable with CS_XCHG_PEER (one NVSwitch box)              */
+
 /* Size in bytes of the per-run device control block (n_sel counter, the two arg-max key
  * slots, ticket, status, separation / viability words).  Zero it with cs_reset_ctl. */
 #define CS_CTL_BYTES 256
@@ -73,7 +79,8 @@ typedef struct cs_ctl_view {
     uint64_t live_rows;  /* rows whose distance the last cs_fps_step evaluated               */
     float last_val;      /* value (max h) of the last committed pick                          */
     int32_t last_idx;    /* global index of the last committed pick (-1: nothing left)       */
-    uint8_t reserved[CS_CTL_BYTES - 56];
+    uint32_t xseq;       /* peer exchange: sequence number of the last published candidate   */
+    uint8_t reserved[CS_CTL_BYTES - 60];
 } cs_ctl_view;
 
 /*
@@ -98,6 +105,13 @@ typedef struct cs_state {
     void* ctl;             /* CS_CTL_BYTES control block                                      */
     uint32_t* pack_local;  /* [4 + D] this rank's candidate (world_size > 1), else NULL       */
     const uint32_t* pack_all; /* [world_size, 4 + D] all-gathered candidates, else NULL       */
+    int32_t rank;          /* this rank (CS_XCHG_PEER)                                        */
+    int32_t xchg;          /* CS_XCHG_GATHER or CS_XCHG_PEER                                  */
+    uint32_t* peer_win[CS_MAX_PEERS]; /* CS_XCHG_PEER: every rank's exchange window as mapped
+                              into THIS process (peer_win[rank] is the local one); each holds
+                              cs_xchg_window_words() zero-initialised 32-bit words             */
+    int32_t xchg_timeout_ms; /* bound of the flag wait (0 = 10 s); on expiry status becomes 3  */
+    int32_t reserved0;
 } cs_state;
 
 typedef void* cs_stream; /* cudaStream_t */
@@ -167,6 +181,19 @@ CS_API int cs_sim_begin(const cs_state* s, float sep, cs_stream stream);
  * best candidate value over all ranks.  Replaces final_viable_check_kernel
  * (kernels/argmax.cu:152-159) and final_viable_check_multi_sharded_kernel (multi.cu:369-384). */
 CS_API int cs_sim_final_check(const cs_state* s, cs_stream stream);
+
+/* Words (32-bit) of one rank's exchange window for CS_XCHG_PEER: 64 flag words followed by two
+ * buffers of world_size candidates (4 + D words each, rounded up to a multiple of 4). */
+CS_API int64_t cs_xchg_window_words(int32_t world_size, int32_t D);
+
+/*
+ * CS_XCHG_PEER only: wait (bounded) until every rank's current candidate has arrived, without
+ * consuming it in a commit.  Needed before publishing again when the last published candidate was
+ * not consumed by cs_commit_bound / cs_sim_final_check (e.g. a forced pick right after a step):
+ * a rank may publish sequence s+1 only after it has seen every peer's sequence s.  No counterpart
+ * in the reference (its exchange is a host-driven all-gather, cuda/multi/fps_sharded.py:171).
+ */
+CS_API int cs_xchg_wait(const cs_state* s, cs_stream stream);
 
 /*
  * Recompute the arg-max key of the NEXT pick (and, for world_size > 1, the candidate pack) from

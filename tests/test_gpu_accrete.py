@@ -50,3 +50,12 @@ def test_accrete_sharded_matches_reference(tmp_path, world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     _launch(world, dict(mode="accrete", cases=[], out_dir=str(tmp_path)), timeout=1500)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_accrete_sharded_peer_exchange_matches_reference(tmp_path, world):
+    from tests.test_gpu_multi import _launch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _launch(world, dict(mode="accrete", cases=[], out_dir=str(tmp_path)), timeout=1500,
+            extra_env={"CORESETS_B200_EXCHANGE": "p2p", "CORESETS_B200_XCHG_TIMEOUT_MS": "5000"})

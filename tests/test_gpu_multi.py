@@ -21,12 +21,12 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _launch(world: int, cfg: dict, timeout: int = 420) -> None:
+def _launch(world: int, cfg: dict, timeout: int = 420, extra_env=None) -> None:
     port = _free_port()
     procs = []
     for r in range(world):
         env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r),
-                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", **(extra_env or {}))
         procs.append(subprocess.Popen([sys.executable, str(ROOT / "tests" / "nccl_worker.py"), json.dumps(cfg)],
                                       env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     outs = []
@@ -70,3 +70,12 @@ def test_fps_sharded_nccl_multi(tmp_path, world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     _launch(world, dict(cases=_cases(world), out_dir=str(tmp_path)))
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fps_sharded_peer_exchange_multi(tmp_path, world):
+    """Same cases with the candidates exchanged by peer stores over NVLink instead of NCCL."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _launch(world, dict(cases=_cases(world), out_dir=str(tmp_path)),
+            extra_env={"CORESETS_B200_EXCHANGE": "p2p", "CORESETS_B200_XCHG_TIMEOUT_MS": "5000"})

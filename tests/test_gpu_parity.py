@@ -287,3 +287,69 @@ def test_engine_reproduces_reference_on_device_generated_workloads(wname, n_rows
     X = MixtureSource(w).rows(0, n_rows, torch.device("cuda:0"))
     sel = fps_mod.fps(X, K)
     np.testing.assert_array_equal(sel.cpu().numpy(), ref)
+
+
+# ---- peer-store exchange (CS_XCHG_PEER) emulated on one device ------------------------------------
+def _peer_engines(X_np, sizes, k, timeout_ms=2000, monkeypatch=None):
+    """W engines on ONE device wired for the peer exchange: every 'rank' gets a window in local
+    memory and all windows are visible to all engines.  Launch order guarantees that a candidate is
+    published before any kernel waits for it, so no kernel ever waits on a later launch."""
+    from coresets_b200._native import XCHG_PEER
+    dev = torch.device("cuda:0")
+    W = len(sizes)
+    offs = np.concatenate([[0], np.cumsum(sizes)[:-1]]).tolist()
+    X = torch.from_numpy(X_np).to(dev)
+    norms = engine.row_norms(X)
+    native = _native.get_native()
+    words = native.xchg_window_words(W, X.shape[1])
+    wins = [torch.zeros(words, dtype=torch.int32, device=dev) for _ in range(W)]
+    if monkeypatch is not None:
+        monkeypatch.setenv("CORESETS_B200_XCHG_TIMEOUT_MS", str(timeout_ms))
+    engs = []
+    for r in range(W):
+        Xl = X[offs[r] : offs[r] + sizes[r]].contiguous()
+        nl = norms[offs[r] : offs[r] + sizes[r]].contiguous()
+        e = engine.ShardEngine(Xl, nl, k, shard_offset=offs[r], world_size=W)
+        e.rank, e.xchg, e.window = r, XCHG_PEER, wins[r]
+        e.peer_ptrs = [w.data_ptr() for w in wins]
+        e.state = e._make_state()
+        e.init_state()
+        engs.append(e)
+    return engs, norms.cpu().numpy(), offs, wins
+
+
+@pytest.mark.parametrize("sizes", [[1000, 1003], [0, 700, 0, 650], [333] * 7 + [340]])
+def test_peer_exchange_kernels_on_one_device(sizes, monkeypatch):
+    N, k = sum(sizes), 120
+    X = with_duplicates(gaussian_mixture(N, 64, 8, seed=N), 50, seed=1)
+    first = N // 3
+    engs, norms, offs, _ = _peer_engines(X, sizes, k, monkeypatch=monkeypatch)
+    for e in engs:
+        e.force_pick(first)                 # every rank publishes ...
+    for i in range(k):
+        for e in engs:
+            e.commit()                      # ... before any rank consumes
+        for e in engs:
+            e.step()
+    o_sel, o_eps, o_h, o_v = oracle.fps_sharded(X, norms, k, sizes, first=first)
+    for r, e in enumerate(engs):
+        ctl = e.check_status()
+        assert ctl.n_sel == k and ctl.xseq == k + 1
+        np.testing.assert_array_equal(e.selected.cpu().numpy(), o_sel)
+        np.testing.assert_array_equal(bits(e.eps.cpu().numpy()), bits(o_eps))
+        n = sizes[r]
+        np.testing.assert_array_equal(bits(e.h[:n].cpu().numpy()), bits(o_h[offs[r] : offs[r] + n]))
+
+
+def test_peer_exchange_wait_times_out_with_a_status(monkeypatch):
+    """A peer that never publishes: the bounded wait gives up, the status word says so, the
+    context stays usable."""
+    X = gaussian_mixture(600, 32, 4, seed=4)
+    engs, _, _, _ = _peer_engines(X, [300, 300], 8, timeout_ms=40, monkeypatch=monkeypatch)
+    e0 = engs[0]
+    e0.force_pick(5)          # rank 1 stays silent
+    e0.commit()
+    with pytest.raises(RuntimeError, match="timed out waiting for a peer"):
+        e0.check_status()
+    # the device still answers
+    assert int(torch.ones(4, device="cuda").sum().item()) == 4

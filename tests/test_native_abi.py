@@ -31,6 +31,6 @@ def test_library_exports_every_declared_symbol():
 
 def test_struct_layouts_match_the_header():
     assert ctypes.sizeof(_native.CtlView) == 256
-    assert ctypes.sizeof(_native.CsState) == 128              # 15 pointers/int64 + two int32
+    assert ctypes.sizeof(_native.CsState) == 128 + 8 + 64 + 8  # + rank/xchg, 8 peer windows, timeout
     assert _native.CsState.D.offset == 48 and _native.CsState.world_size.offset == 52
     assert _native.CtlView.live_rows.offset == 40 and _native.CtlView.last_idx.offset == 52
