@@ -311,7 +311,10 @@ def run_ours(args):
             "config": {"workload": f"{w.name}: {w.describe}", "rows": w.n_rows, "dim": w.dim,
                        "rows_per_gpu": max(sizes), "mode": "dense", "first_pick": 0,
                        "l2": "inputs (>= 19 GB per GPU) exceed the 126 MB L2; no flush",
-                       "exchange": "one NCCL all-gather of (4+D) words per rank per pick" if world > 1 else "none",
+                       "exchange": ("none" if world == 1 else
+                                    "peer stores over NVLink + flag wait, fused into the two kernels"
+                                    if engine.exchange_mode() == "p2p" else
+                                    "one NCCL all-gather of (4+D) words per rank per pick"),
                        "generate_s": round(t_gen, 2), "sms": sms},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "traffic": None, "kernel": "fps_step_kernel (dense)",
