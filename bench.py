@@ -291,7 +291,8 @@ def run_ours(args):
     # ---- end to end through the public API: host X -> device -> picks -> host -----------------
     e2e = None
     if not args.no_e2e:
-        del eng, norms
+        eng = None
+        norms = None
         torch.cuda.empty_cache()
         try:
             e2e = run_e2e(args, X, w, world, rank, device, K, W, off)

@@ -13,7 +13,7 @@ from typing import Optional
 
 from . import build as _build
 
-CS_ABI_VERSION = 2
+CS_ABI_VERSION = 3
 CS_CTL_BYTES = 256
 
 MODE_PRUNE = 0

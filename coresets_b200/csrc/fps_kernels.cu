@@ -40,7 +40,12 @@ enum { ST_CAPACITY = 1, ST_FORCE_NOT_OWNED = 2, ST_XCHG_TIMEOUT = 3 };
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr unsigned kFull = 0xffffffffu;
-constexpr int kRowsPerLane = 4;          // a warp walks super-tiles of 32 * 4 = 128 consecutive rows
+#ifndef CS_RPL
+#define CS_RPL 4
+#endif
+constexpr int kRowsPerLane = CS_RPL;     // a warp walks super-tiles of 32 * kRowsPerLane consecutive rows (4 or 2)
+constexpr int kTileShift = CS_RPL == 4 ? 7 : 6;
+static_assert(CS_RPL == 4 || CS_RPL == 2, "rows per lane");
 #ifndef CS_INFLIGHT
 #define CS_INFLIGHT 8
 #endif
@@ -354,8 +359,13 @@ __device__ __forceinline__ void tile_rows(const float4* __restrict__ X4, const i
 }
 
 template <int CPL, bool FULL>
-__global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const cs_state s, const unsigned mode) {
-    extern __shared__ __align__(16) float s_cen[];       // generic path only
+__global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const cs_state s, const unsigned mode,
+                                                                           const int n_bound_smem) {
+    // dynamic shared memory: the first n_bound_smem triangle bounds (the per-row bound lookup is
+    // then a shared-memory read instead of an L2 round trip), then the centre on the generic path
+    extern __shared__ __align__(16) float s_dyn[];
+    float* s_dsl = s_dyn;
+    float* s_cen = s_dyn + n_bound_smem;
     __shared__ u64 s_keys[kWarps];
     __shared__ unsigned s_live[kWarps];
     __shared__ int s_last;
@@ -383,62 +393,83 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
             cen[c] = (FULL || lane + 32 * c < d4) ? c4[lane + 32 * c] : make_float4(0.f, 0.f, 0.f, 0.f);
     } else {
         for (int c = threadIdx.x; c < D; c += blockDim.x) s_cen[c] = cen_g[c];
-        __syncthreads();
     }
+    const int nb = i < n_bound_smem ? i : n_bound_smem;
+    for (int c = threadIdx.x; c < nb; c += blockDim.x) s_dsl[c] = s.dSL_quarter[c];
+    __syncthreads();
 
     const int64_t N = s.N_local;
-    const int64_t tiles = (N + 127) >> 7;
-    const int64_t nw = (int64_t)gridDim.x * kWarps;
+    constexpr int R = kRowsPerLane;
+    const int n32 = (int)N;                                  // local rows fit 31 bits (validated)
+    const int tiles = (int)((N + (32 * R - 1)) >> kTileShift);
+    const int whole_tiles = (int)(N >> kTileShift);          // super-tiles whose rows all exist
+    const int nw = (int)gridDim.x * kWarps;
     const float4* X4 = reinterpret_cast<const float4*>(s.X);
     const bool vec_ok = ((((uintptr_t)s.h) | ((uintptr_t)s.voronoi) | ((uintptr_t)s.norms)) & 15u) == 0;
-    u64 best = 0;
+    const float kNegInf = __uint_as_float(0xff800000u);
+    // Per-lane running arg-max as (value, local row); the 64-bit key is built once at the end.
+    // NaN never wins (comparisons are false), -0.0 == +0.0, as in argmax_better.
+    float best_h = kNegInf;
+    int best_row = -1;
     unsigned live_cnt = 0;
 
-    for (int64_t t = (int64_t)blockIdx.x * kWarps + warp; t < tiles; t += nw) {
-        // lane j owns rows r0 .. r0+3: one 16-byte load each for h and voronoi (coalesced 512 B)
-        const int64_t base = t << 7;
-        const int64_t r0 = base + 4 * lane;
-        float hq[4];
-        unsigned updbits = 0;                // bit j: row r0+j may be updated
-        unsigned m[4];
-        const bool whole = vec_ok && (r0 + 3 < N);
-        {
-            int vq[4] = {0, 0, 0, 0};
-            if (whole) {
-                const float4 h4 = *reinterpret_cast<const float4*>(s.h + r0);
-                hq[0] = h4.x; hq[1] = h4.y; hq[2] = h4.z; hq[3] = h4.w;
+    // ---- full treatment of one super-tile: predicate, row walk, update, arg-max ---------------
+    // Lane j owns rows r0 .. r0+R-1 (one vector load each for h and voronoi, coalesced).  Rows
+    // past the end read as -inf: not live, never above the running maximum.
+    auto full_tile = [&](const int t) {
+        const int r0 = (t << kTileShift) + R * lane;
+        float hq[R];
+        int vq[R];
+        if (vec_ok && t < whole_tiles) {
+            if (R == 4) {
+                const float4 a = *reinterpret_cast<const float4*>(s.h + r0);
+                hq[0] = a.x; hq[1] = a.y; hq[R - 2] = a.z; hq[R - 1] = a.w;
                 if (!first) {
-                    const int4 v4 = *reinterpret_cast<const int4*>(s.voronoi + r0);
-                    vq[0] = v4.x; vq[1] = v4.y; vq[2] = v4.z; vq[3] = v4.w;
+                    const int4 b = *reinterpret_cast<const int4*>(s.voronoi + r0);
+                    vq[0] = b.x; vq[1] = b.y; vq[R - 2] = b.z; vq[R - 1] = b.w;
                 }
             } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const bool in = r0 + j < N;
-                    hq[j] = in ? s.h[r0 + j] : -1.0f;
-                    vq[j] = (in && !first) ? s.voronoi[r0 + j] : 0;
+                const float2 a = *reinterpret_cast<const float2*>(s.h + r0);
+                hq[0] = a.x; hq[1] = a.y;
+                if (!first) {
+                    const int2 b = *reinterpret_cast<const int2*>(s.voronoi + r0);
+                    vq[0] = b.x; vq[1] = b.y;
                 }
             }
-            float bound[4];
+        } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const bool live = (r0 + j < N) && !(hq[j] < 0.0f);        // warp.cu:28-30, 75-77
-                bound[j] = (live && !first) ? __ldg(s.dSL_quarter + vq[j]) : 0.0f;
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const bool live = (r0 + j < N) && !(hq[j] < 0.0f);
-                const bool up = live && (first || !(bound[j] >= hq[j]));   // warp.cu:80-82
-                updbits |= (up ? 1u : 0u) << j;
-                m[j] = __ballot_sync(kFull, dense ? live : up);
-                live_cnt += __popc(m[j]);
+            for (int j = 0; j < R; ++j) {
+                const bool in = r0 + j < n32;
+                hq[j] = in ? s.h[r0 + j] : kNegInf;
+                vq[j] = (in && !first) ? s.voronoi[r0 + j] : 0;
             }
         }
-        float dots[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        bool up[R], need[R];
+        bool any_need = false;
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            const bool live = !(hq[j] < 0.0f);                             // warp.cu:28-30, 75-77
+            up[j] = live;
+            if (!first && live) {
+                const float b = (vq[j] < nb) ? s_dsl[vq[j]] : __ldg(s.dSL_quarter + vq[j]);
+                up[j] = !(b >= hq[j]);                                     // warp.cu:80-82
+            }
+            need[j] = dense ? live : up[j];
+            any_need |= need[j];
+        }
+        if (__any_sync(kFull, any_need)) {                   // most super-tiles need nothing in prune mode
+        const int64_t base = (int64_t)t << kTileShift;
+        float dots[R];
+#pragma unroll
+        for (int j = 0; j < R; ++j) dots[j] = 0.0f;
 #pragma unroll 1
-        for (int j = 0; j < 4; ++j) {       // one copy of the row walk, not four (register budget)
-            const unsigned mj = j == 0 ? m[0] : j == 1 ? m[1] : j == 2 ? m[2] : m[3];
+        for (int j = 0; j < R; ++j) {        // one copy of the row walk, not R (register budget)
+            bool nj = need[0];
+#pragma unroll
+            for (int q = 1; q < R; ++q) nj = (j == q) ? need[q] : nj;
+            const unsigned mj = __ballot_sync(kFull, nj);
             if (!mj) continue;
+            live_cnt += __popc(mj);
             float dj = 0.0f;
             if (CPL) {
                 tile_rows<CPL, FULL>(X4, base + j, d4, mj, cen, lane, dj);
@@ -451,37 +482,35 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
                     if (lane == r) dj = p;
                 }
             }
-            if (j == 0) dots[0] = dj; else if (j == 1) dots[1] = dj; else if (j == 2) dots[2] = dj; else dots[3] = dj;
+#pragma unroll
+            for (int q = 0; q < R; ++q) dots[q] = (j == q) ? dj : dots[q];
         }
-        if (updbits) {
-            float nq[4];
-            if (whole && dense) {
-                const float4 n4 = __ldg(reinterpret_cast<const float4*>(s.norms + r0));
-                nq[0] = n4.x; nq[1] = n4.y; nq[2] = n4.z; nq[3] = n4.w;
-            } else {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) nq[j] = ((updbits >> j) & 1u) ? __ldg(s.norms + r0 + j) : 0.0f;
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if ((updbits >> j) & 1u) {
-                    const float d = sq_dist(nq[j], nn, dots[j]);
-                    if (d < hq[j]) {
-                        hq[j] = d;
-                        s.h[r0 + j] = d;
-                        s.voronoi[r0 + j] = i;
-                    }
+        for (int j = 0; j < R; ++j) {
+            if (up[j]) {
+                const float d = sq_dist(__ldg(s.norms + r0 + j), nn, dots[j]);
+                if (d < hq[j]) {
+                    hq[j] = d;
+                    s.h[r0 + j] = d;
+                    s.voronoi[r0 + j] = i;
                 }
             }
         }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (r0 + j < N) {
-                const u64 k = make_key(hq[j], s.shard_offset + r0 + j);
-                best = k > best ? k : best;
-            }
         }
-    }
+        // running arg-max: a lane meets its rows in increasing order, so a strict '>' keeps the
+        // smallest row among equal values; the row is resolved only on improvement
+        float tmax = hq[0];
+#pragma unroll
+        for (int j = 1; j < R; ++j) tmax = fmaxf(tmax, hq[j]);
+        if (tmax > best_h) {
+            best_h = tmax;
+#pragma unroll
+            for (int j = R - 1; j >= 0; --j) best_row = (hq[j] == tmax) ? r0 + j : best_row;
+        }
+    };
+
+    for (int t = (int)blockIdx.x * kWarps + warp; t < tiles; t += nw) full_tile(t);
+    u64 best = best_row >= 0 ? make_key(best_h, s.shard_offset + best_row) : 0;
 
     best = warp_max_key(best);
     if (lane == 0) { s_keys[warp] = best; s_live[warp] = live_cnt; }
@@ -644,31 +673,37 @@ int validate(const cs_state* s) {
     return CS_OK;
 }
 
+constexpr int kBoundSmemMax = 16384;     // triangle bounds staged in shared memory (64 KB)
+
 template <int CPL, bool FULL>
 int launch_step(const cs_state* s, unsigned mode, cudaStream_t st, int sms) {
-    static thread_local int bps = 0;
-    const size_t smem = CPL ? 0 : (size_t)s->D * sizeof(float);
-    if (CPL == 0 && smem > 48 * 1024) {
+    static thread_local size_t attr_set = 0, occ_smem = ~(size_t)0;
+    static thread_local int occ_blocks = 0;
+    const int n_bound = (int)(s->cap < kBoundSmemMax ? s->cap : kBoundSmemMax);
+    const size_t smem = (size_t)n_bound * sizeof(float) + (CPL ? 0 : (size_t)s->D * sizeof(float));
+    if (smem > 48 * 1024 && smem > attr_set) {
         if (cudaFuncSetAttribute(fps_step_kernel<CPL, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) {
             g_last_cuda = cudaGetLastError();
             return CS_E_LAUNCH;
         }
+        attr_set = smem;
     }
-    int per_sm = bps;
-    if (CPL == 0 || per_sm == 0) {
+    if (occ_smem != smem) {
+        int per_sm = 0;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fps_step_kernel<CPL, FULL>, kThreads, smem) !=
                 cudaSuccess || per_sm < 1) {
             g_last_cuda = cudaGetLastError();
             return CS_E_LAUNCH;
         }
-        if (CPL) bps = per_sm;
+        occ_blocks = per_sm;
+        occ_smem = smem;
     }
-    const int64_t tiles = (s->N_local + 127) >> 7;
+    const int64_t tiles = (s->N_local + (32 * kRowsPerLane - 1)) >> kTileShift;
     int64_t want = (tiles + kWarps - 1) / kWarps;
-    int64_t cap = (int64_t)sms * per_sm;         // persistent grid: a multiple of the SM count
+    int64_t cap = (int64_t)sms * occ_blocks;     // persistent grid: a multiple of the SM count
     int grid = (int)(want < 1 ? 1 : (want < cap ? want : cap));
-    fps_step_kernel<CPL, FULL><<<grid, kThreads, smem, st>>>(*s, mode);
+    fps_step_kernel<CPL, FULL><<<grid, kThreads, smem, st>>>(*s, mode, n_bound);
     return check_launch();
 }
 

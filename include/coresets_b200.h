@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define CS_ABI_VERSION 2
+#define CS_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define CS_API __attribute__((visibility("default")))
