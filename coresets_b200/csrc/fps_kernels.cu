@@ -540,6 +540,159 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
     }
 }
 
+// ---- several probes in one pass over X ("lanes") ------------------------------------------------
+// L independent states (own h, voronoi, centre table, control block) share X and norms.  A warp
+// owns tiles of 32 consecutive rows; lane j of the warp holds, for every state, h / voronoi of row
+// base + j and that state's predicate.  A row is loaded ONCE if any state needs its distance and
+// is dotted with every interested state's centre (centres in shared memory), with exactly the
+// arithmetic of fps_step_kernel, so every state ends bit-identical to a separate cs_fps_step.
+struct LaneSet {
+    cs_state s[CS_MAX_LANES];
+};
+
+template <int L, int CPL>
+__global__ void __launch_bounds__(kThreads, 2) fps_step_lanes_kernel(const LaneSet ls, const unsigned mode) {
+    extern __shared__ __align__(16) float s_cen[];           // [L][D]
+    __shared__ u64 s_keys[L][kWarps];
+    __shared__ int s_last;
+    const int D = ls.s[0].D;
+    const int d4 = D >> 2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool dense = (mode & CS_MODE_DENSE) != 0;
+
+    Ctl* ctl[L];
+    int pick[L];
+    float nn[L];
+    bool on[L];
+#pragma unroll
+    for (int l = 0; l < L; ++l) {
+        ctl[l] = reinterpret_cast<Ctl*>(ls.s[l].ctl);
+        pick[l] = ctl[l]->n_sel;
+        on[l] = pick[l] < ls.s[l].cap;
+        if (!on[l] && blockIdx.x == 0 && threadIdx.x == 0) ctl[l]->status = ST_CAPACITY;
+        nn[l] = on[l] ? ls.s[l].norms_sel[pick[l]] : 0.0f;
+        if (on[l]) {
+            const float* cg = ls.s[l].X_sel + (int64_t)pick[l] * D;
+            for (int c = threadIdx.x; c < D; c += blockDim.x) s_cen[l * D + c] = cg[c];
+        }
+    }
+    __syncthreads();
+
+    const int64_t N = ls.s[0].N_local;
+    const int n32 = (int)N;
+    const int tiles = (int)((N + 31) >> 5);
+    const int nw = (int)gridDim.x * kWarps;
+    const float4* X4 = reinterpret_cast<const float4*>(ls.s[0].X);
+    const float* norms = ls.s[0].norms;
+    const float kNegInf = __uint_as_float(0xff800000u);
+    float best_h[L];
+    int best_row[L];
+#pragma unroll
+    for (int l = 0; l < L; ++l) { best_h[l] = kNegInf; best_row[l] = -1; }
+
+    for (int t = (int)blockIdx.x * kWarps + warp; t < tiles; t += nw) {
+        const int row = (t << 5) + lane;
+        const bool valid = row < n32;
+        float hq[L];
+        bool up[L];
+        unsigned m[L];
+        unsigned uni = 0;
+#pragma unroll
+        for (int l = 0; l < L; ++l) {
+            hq[l] = (valid && on[l]) ? ls.s[l].h[row] : kNegInf;
+            const bool live = !(hq[l] < 0.0f);                              // warp.cu:28-30, 75-77
+            up[l] = live;
+            if (live && pick[l] > 0) {
+                const int v = ls.s[l].voronoi[row];
+                up[l] = !(__ldg(ls.s[l].dSL_quarter + v) >= hq[l]);         // warp.cu:80-82
+            }
+            m[l] = __ballot_sync(kFull, dense ? live : up[l]);
+            uni |= m[l];
+        }
+        float dots[L];
+#pragma unroll
+        for (int l = 0; l < L; ++l) dots[l] = 0.0f;
+        constexpr int RB = CPL >= 4 ? 1 : (4 / CPL);        // rows whose loads are in flight together
+        while (uni) {
+            int rows[RB];
+            float4 a[RB][CPL];
+#pragma unroll
+            for (int b = 0; b < RB; ++b) {
+                rows[b] = uni ? (__ffs(uni) - 1) : -1;
+                uni &= uni - 1;
+            }
+#pragma unroll
+            for (int b = 0; b < RB; ++b) {
+                if (rows[b] >= 0) {
+                    const float4* rp = X4 + ((int64_t)(t << 5) + rows[b]) * (int64_t)d4 + lane;
+#pragma unroll
+                    for (int c = 0; c < CPL; ++c)
+                        if (lane + 32 * c < d4) a[b][c] = ld_stream4(rp + 32 * c);
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < RB; ++b) {
+                if (rows[b] < 0) continue;
+#pragma unroll
+                for (int l = 0; l < L; ++l) {
+                    if (!((m[l] >> rows[b]) & 1u)) continue;                // warp-uniform
+                    const float4* c4 = reinterpret_cast<const float4*>(s_cen + l * D);
+                    float p = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < CPL; ++c)
+                        if (lane + 32 * c < d4) p = __fadd_rn(p, chunk_dot(a[b][c], c4[lane + 32 * c]));
+                    p = warp_tree_sum(p);
+                    if (lane == rows[b]) dots[l] = p;
+                }
+            }
+        }
+        const float nrow = valid ? __ldg(norms + row) : 0.0f;
+#pragma unroll
+        for (int l = 0; l < L; ++l) {
+            if (up[l]) {
+                const float d = sq_dist(nrow, nn[l], dots[l]);
+                if (d < hq[l]) {
+                    hq[l] = d;
+                    ls.s[l].h[row] = d;
+                    ls.s[l].voronoi[row] = pick[l];
+                }
+            }
+            if (hq[l] > best_h[l]) { best_h[l] = hq[l]; best_row[l] = row; }   // rows come in order
+        }
+    }
+
+#pragma unroll
+    for (int l = 0; l < L; ++l) {
+        u64 k = best_row[l] >= 0 ? make_key(best_h[l], ls.s[l].shard_offset + best_row[l]) : 0;
+        k = warp_max_key(k);
+        if (lane == 0) s_keys[l][warp] = k;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int l = 0; l < L; ++l) {
+            u64 bk = 0;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) bk = s_keys[l][w] > bk ? s_keys[l][w] : bk;
+            if (bk && on[l]) atomicMax(&ctl[l]->key[(pick[l] + 1) & 1], bk);
+        }
+        __threadfence();
+        s_last = (atomicAdd(&ctl[0]->ticket, 1u) == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+#pragma unroll
+    for (int l = 0; l < L; ++l) {
+        if (!on[l]) continue;
+        const u64 k = *reinterpret_cast<volatile u64*>(&ctl[l]->key[(pick[l] + 1) & 1]);
+        if (ls.s[l].world_size > 1) publish_candidate(ls.s[l], ctl[l], k, key_idx(k) - ls.s[l].shard_offset);
+        __syncthreads();
+        if (threadIdx.x == 0) ctl[l]->n_sel = pick[l] + 1;
+    }
+    if (threadIdx.x == 0) ctl[0]->ticket = 0;
+}
+
 // ---- small single-block kernels ---------------------------------------------------------------
 __global__ void init_state_kernel(float* h, int32_t* v, int64_t N, Ctl* ctl) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -707,6 +860,48 @@ int launch_step(const cs_state* s, unsigned mode, cudaStream_t st, int sms) {
     return check_launch();
 }
 
+template <int L, int CPL>
+int launch_lanes_t(const LaneSet& ls, unsigned mode, cudaStream_t st, int sms) {
+    const size_t smem = (size_t)L * ls.s[0].D * sizeof(float);
+    static thread_local int per_sm = 0;
+    if (per_sm == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fps_step_lanes_kernel<L, CPL>, kThreads, smem) !=
+                cudaSuccess || per_sm < 1) {
+            g_last_cuda = cudaGetLastError();
+            per_sm = 0;
+            return CS_E_LAUNCH;
+        }
+    }
+    const int64_t tiles = (ls.s[0].N_local + 31) >> 5;
+    int64_t want = (tiles + kWarps - 1) / kWarps;
+    int64_t cap = (int64_t)sms * per_sm;
+    int grid = (int)(want < 1 ? 1 : (want < cap ? want : cap));
+    fps_step_lanes_kernel<L, CPL><<<grid, kThreads, smem, st>>>(ls, mode);
+    return check_launch();
+}
+
+template <int L>
+int launch_lanes_l(const LaneSet& ls, unsigned mode, cudaStream_t st, int sms) {
+    const int D = ls.s[0].D;
+    if (D <= 128) return launch_lanes_t<L, 1>(ls, mode, st, sms);
+    if (D <= 256) return launch_lanes_t<L, 2>(ls, mode, st, sms);
+    if (D <= 512) return launch_lanes_t<L, 4>(ls, mode, st, sms);
+    return launch_lanes_t<L, 8>(ls, mode, st, sms);
+}
+
+int launch_lanes(const LaneSet& ls, int n, unsigned mode, cudaStream_t st, int sms) {
+    switch (n) {
+        case 2: return launch_lanes_l<2>(ls, mode, st, sms);
+        case 3: return launch_lanes_l<3>(ls, mode, st, sms);
+        case 4: return launch_lanes_l<4>(ls, mode, st, sms);
+        case 5: return launch_lanes_l<5>(ls, mode, st, sms);
+        case 6: return launch_lanes_l<6>(ls, mode, st, sms);
+        case 7: return launch_lanes_l<7>(ls, mode, st, sms);
+        case 8: return launch_lanes_l<8>(ls, mode, st, sms);
+        default: return CS_E_ARG;
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -849,13 +1044,29 @@ int cs_scan_argmax(const cs_state* s, cs_stream stream) {
 }
 
 int cs_fps_step_lanes(const cs_state* lanes, int32_t n_lanes, uint32_t mode, cs_stream stream) {
-    if (!lanes || n_lanes < 1 || n_lanes > 8) return CS_E_ARG;
-    // each lane's arithmetic is exactly cs_fps_step's; lanes are issued back to back
+    if (!lanes || n_lanes < 1 || n_lanes > CS_MAX_LANES || mode > CS_MODE_DENSE) return CS_E_ARG;
     for (int l = 0; l < n_lanes; ++l) {
-        int rc = cs_fps_step(&lanes[l], mode, stream);
+        int rc = validate(&lanes[l]);
         if (rc) return rc;
+        if (lanes[l].X != lanes[0].X || lanes[l].norms != lanes[0].norms || lanes[l].N_local != lanes[0].N_local ||
+            lanes[l].D != lanes[0].D || lanes[l].shard_offset != lanes[0].shard_offset)
+            return CS_E_ARG;                   // lanes share the matrix; only their state differs
     }
-    return CS_OK;
+    const int D = lanes[0].D;
+    // one lane, rows that are not 16-byte chunks, or very wide rows: the single-state kernel per lane
+    if (n_lanes == 1 || (D & 3) != 0 || D > 1024 || lanes[0].N_local == 0) {
+        for (int l = 0; l < n_lanes; ++l) {
+            int rc = cs_fps_step(&lanes[l], mode, stream);
+            if (rc) return rc;
+        }
+        return CS_OK;
+    }
+    DevInfo d = device_info();
+    if (!d.ok) return CS_E_DEVICE;
+    LaneSet ls;
+    for (int l = 0; l < n_lanes; ++l) ls.s[l] = lanes[l];
+    for (int l = n_lanes; l < CS_MAX_LANES; ++l) ls.s[l] = lanes[0];
+    return launch_lanes(ls, n_lanes, mode, (cudaStream_t)stream, d.sms);
 }
 
 }  // extern "C"

@@ -171,7 +171,7 @@ class AccreteDriver:
         self.selected_set = set(snap.selected)
         self.sep = snap.sep
 
-    def _reconstruct(self, snap: _Snapshot, added_t: Tensor, sel_start_t: Tensor, m: int) -> None:
+    def _reconstruct(self, snap: _Snapshot, added_t: Tensor, sel_start_t: Tensor, m: int, target=None) -> None:
         """State after keeping only the first ``m`` forward picks, written into the simulation
         engine's ``h`` / ``voronoi``.  Rows whose final centre lies in the dropped tail are
         recomputed against the kept picks with the reference's expression
@@ -179,7 +179,8 @@ class AccreteDriver:
         _shared.py:67-152), so the values are the ones the reference feeds its simulations."""
         n_snap = snap.n_selected
         n = self.layout.N_shard
-        h_mid, v_mid = self.S.h, self.S.voronoi
+        target = self.S if target is None else target
+        h_mid, v_mid = target.h, target.voronoi
         h_mid.copy_(self.h_final)
         v_mid.copy_(self.v_final)
         if n > 0:
@@ -215,18 +216,16 @@ class AccreteDriver:
             if mine.numel() > 0:
                 h_mid[mine] = -1.0
 
-    def _simulate(self, sep_mid: float, points_left: int, n_init: int) -> Tuple[bool, int]:
-        """One bisect probe on the simulation engine's state: up to ``points_left`` unrestricted
-        picks, viable as soon as the running separation beats the coverage
-        (simulate.cu:10-90, multi.cu:428-528)."""
-        S = self.S
+    def _sim_start(self, S, sep_mid: float, n_init: int) -> None:
         if n_init > 0:
             S.X_sel[:n_init].copy_(self.E.X_sel[:n_init])
             S.norms_sel[:n_init].copy_(self.E.norms_sel[:n_init])
         S.reset_ctl(n_init)
         S.sim_begin(sep_mid)
         S.scan()
-        done = 0
+
+    def _sim_finish(self, S, done: int, points_left: int) -> Tuple[bool, int]:
+        """Run a started probe from ``done`` (a multiple of 16) picks to its verdict."""
         while done < points_left:
             n = min(_SIM_POLL, points_left - done)
             S.run_picks(n, self.rules)
@@ -236,6 +235,49 @@ class AccreteDriver:
         S.exchange()
         S.sim_final_check()
         return bool(S.check_status().viable), points_left
+
+    def _simulate(self, sep_mid: float, points_left: int, n_init: int) -> Tuple[bool, int]:
+        """One bisect probe on the simulation engine's state: up to ``points_left`` unrestricted
+        picks, viable as soon as the running separation beats the coverage
+        (simulate.cu:10-90, multi.cu:428-528)."""
+        self._sim_start(self.S, sep_mid, n_init)
+        return self._sim_finish(self.S, 0, points_left)
+
+    def _lane_engines(self, n: int):
+        """Simulation engines for fused probes; lane 0 is the sequential one.  The count is capped
+        by CORESETS_LANES_MEM_GB (default 8) like the reference's lane scratch (sharded.py:78-97)."""
+        if not hasattr(self, "_lanes"):
+            self._lanes = [self.S]
+        budget = float(os.environ.get("CORESETS_LANES_MEM_GB", "8")) * (1 << 30)
+        per_lane = max(self.layout.sizes) * 8 + self.max_sel * (self.dim * 4 + 12)
+        n = max(1, min(n, 1 + int(budget // max(per_lane, 1))))
+        world = self.layout.world_size if self.multi else 1
+        while len(self._lanes) < n:
+            self._lanes.append(_engine.ShardEngine(self.E.X, self.E.norms, self.max_sel, record=False,
+                                                   shard_offset=self.layout.shard_offset, world_size=world))
+        return self._lanes[:n]
+
+    def _simulate_lanes(self, engines, probes) -> List[bool]:
+        """Several probes as lanes of one loop: one pass over X per step serves them all
+        (multi.cu:800-1019).  Every lane polls its flag after each 16 picks like a lone probe, so
+        each verdict is the lone probe's verdict."""
+        W = len(probes)
+        for S, p in zip(engines, probes):
+            self._sim_start(S, float(p["sep"]), p["n_init"])
+        left = [p["points_left"] for p in probes]
+        verdict: List[Optional[bool]] = [None] * W
+        active = list(range(W))
+        done = 0
+        while len(active) >= 2 and min(left[w] for w in active) - done >= _SIM_POLL:
+            _engine.ShardEngine.run_lane_picks([engines[w] for w in active], _SIM_POLL, self.rules)
+            done += _SIM_POLL
+            for w in list(active):
+                if engines[w].read_ctl().viable:
+                    verdict[w] = True
+                    active.remove(w)
+        for w in active:                      # tails (and a lone survivor) finish on their own
+            verdict[w], _ = self._sim_finish(engines[w], done, left[w])
+        return [bool(v) for v in verdict]
 
     def _fill(self, budget: int, k: int) -> int:
         """Unrestricted FPS for ``budget`` picks (hot loop C).  Same picks in the same order as the
@@ -406,7 +448,7 @@ class AccreteDriver:
 
         memo: Dict[int, bool] = {}
 
-        def classify(mid: int):
+        def classify(mid: int, target=None):
             if mid > ctx["n_added"]:
                 if extend_to is not None and extend_to(mid) > ctx["n_added"]:
                     refresh()
@@ -420,9 +462,9 @@ class AccreteDriver:
             # _base.py:574-597 is N_global minus the prefix length)
             if points_left >= self.n_global - (snap.n_selected + mid):
                 return True
-            self._reconstruct(snap, ctx["added_t"], sel_start_t, mid)
+            self._reconstruct(snap, ctx["added_t"], sel_start_t, mid, target)
             if points_left == 0:
-                return sep_mid > self._global_max(self.S.h)
+                return sep_mid > self._global_max((target or self.S).h)
             return {"sep": sep_mid, "points_left": points_left, "n_init": snap.n_selected + mid}
 
         def viable(mid: int) -> bool:
@@ -445,6 +487,29 @@ class AccreteDriver:
         deep_walk = self.gallop_deep and self._has_seed and self._pos >= 1
         if self.bisect_seeded and (self._bisect_seed <= search.GALLOP_MAX_SEED or deep_walk):
             high = max_add if extend_to is not None else ctx["n_added"]
+            seed = max(0, min(int(self._bisect_seed), high))
+            first_probe = seed if seed > 0 else 1            # the walk never probes m = 0
+            # the walk's first probes as fused lanes; the walk then reads the memo (_base.py:702-726)
+            if self.bisect_lanes >= 2 and total_budget - seed >= self.lanes_min_steps:
+                engines = self._lane_engines(self.bisect_lanes)
+                probes, mids = [], []
+                for mid in range(first_probe, min(first_probe + len(engines), high + 1)):
+                    if mid in memo:
+                        continue
+                    probe = classify(mid, engines[len(probes)])
+                    if isinstance(probe, bool):
+                        memo[mid] = probe
+                    else:
+                        probes.append(probe)
+                        mids.append(mid)
+                if len(probes) >= 2:
+                    t0 = time.perf_counter()
+                    for mid, ok in zip(mids, self._simulate_lanes(engines[: len(probes)], probes)):
+                        memo[mid] = ok
+                        self._n_probe += 1
+                    if self.chatty:
+                        print(f"    [bisect] k={self._k} pos={self._pos} lanes mids={mids} -> "
+                              f"{[memo[m_] for m_ in mids]} ({time.perf_counter() - t0:.1f}s)", flush=True)
             return search.largest_true(viable, high, self._bisect_seed)
         return search.binary_search(viable, ctx["n_added"])
 

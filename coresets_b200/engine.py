@@ -276,6 +276,45 @@ class ShardEngine:
         for _ in range(n):
             self._pick_body(rules)
 
+    # -- several states in one pass over X ("lanes") --------------------------------------------------
+    @staticmethod
+    def step_lanes(engines, mode: Optional[int] = None) -> None:
+        """One fused step for several engines that share ``X`` (bisect probes): ``X`` is streamed
+        once, every engine ends exactly as after its own ``step()``."""
+        e0 = engines[0]
+        arr = (CsState * len(engines))(*[e.state for e in engines])
+        e0.native.fps_step_lanes(arr, len(engines), e0.mode if mode is None else int(mode), e0._stream())
+        for e in engines:
+            e._unconsumed = True
+
+    @staticmethod
+    def run_lane_picks(engines, n: int, rules: int) -> None:
+        """``n`` lock-step picks on every engine of ``engines`` (graph-replayed on the GPU)."""
+        e0 = engines[0]
+
+        def body():
+            for e in engines:
+                e.exchange()
+                e.commit(rules)
+            ShardEngine.step_lanes(engines)
+
+        if not (e0.on_cuda and _graphs_enabled()):
+            for _ in range(n):
+                body()
+            return
+        key = ("lanes", tuple(id(e) for e in engines), n, rules, e0.mode)
+        g = e0._graphs.get(key)
+        if g is None:
+            torch.cuda.synchronize(e0.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                for _ in range(n):
+                    body()
+            e0._graphs[key] = g
+        g.replay()
+        for e in engines:
+            e._unconsumed = True
+
     # -- read-back -----------------------------------------------------------------------------------
     def read_ctl(self) -> CtlView:
         """Copy the control block to the host (synchronises the current stream)."""

@@ -62,6 +62,7 @@ extern "C" {
 #define CS_XCHG_PEER 1     /* cs_fps_step stores the candidate into every rank's exchange window
                               over NVLink and raises a flag; cs_commit_bound waits on the flags   */
 #define CS_MAX_PEERS 8     /* ranks addressable with CS_XCHG_PEER (one NVSwitch box)              */
+#define CS_MAX_LANES 8     /* states one cs_fps_step_lanes call can serve                         */
 
 /* Size in bytes of the per-run device control block (n_sel counter, the two arg-max key
  * slots, ticket, status, separation / viability words).  Zero it with cs_reset_ctl. */

@@ -62,7 +62,7 @@ def accrete_mode(cfg, rank, world) -> None:
     out = Path(cfg["out_dir"])
     try:
         for case in cfg["cases"]:
-            for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK"):
+            for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK", "CORESETS_LANES_MIN_STEPS"):
                 os.environ.pop(k, None)
             os.environ.update(case.get("env", {}))
             X = np.load(case["x_path"])

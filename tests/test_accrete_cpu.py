@@ -59,12 +59,16 @@ def test_sharded_driver_matches_reference(tmp_path, world):
                     n_anchor=c["n_anchor"], max_k=c["max_k"], n_target=c.get("n_target"))
         cases.append(dict(base, name=f"{name}_plain"))
         cases.append(dict(base, name=f"{name}_knobs", env={"CORESETS_BISECT_SEED": "1", "CORESETS_FILL_CHUNK": "256"}))
+        # fused probe lanes forced on (they need long simulations by default): same list as without
+        cases.append(dict(base, name=f"{name}_lanes", env={"CORESETS_BISECT_SEED": "1", "CORESETS_FILL_CHUNK": "256",
+                                                          "CORESETS_LANES_MIN_STEPS": "4"}))
     _run(world, dict(mode="accrete", cases=cases, out_dir=str(tmp_path)), timeout=900)
     for name in CASES:
         z = np.load(GOLDEN / f"accrete_cpu_{name}.npz")
         for r in range(world):
             np.testing.assert_array_equal(np.load(tmp_path / f"{name}_plain_{r}.npy"), z[f"sharded_w{world}"])
             np.testing.assert_array_equal(np.load(tmp_path / f"{name}_knobs_{r}.npy"), z[f"sharded_w{world}_knobs"])
+            np.testing.assert_array_equal(np.load(tmp_path / f"{name}_lanes_{r}.npy"), z[f"sharded_w{world}_knobs"])
 
 
 def test_accrete_validation(fake_native):

@@ -353,3 +353,40 @@ def test_peer_exchange_wait_times_out_with_a_status(monkeypatch):
         e0.check_status()
     # the device still answers
     assert int(torch.ones(4, device="cuda").sum().item()) == 4
+
+
+# ---- fused multi-state step ("lanes") -------------------------------------------------------------
+@pytest.mark.parametrize("N,D,L", [(5000, 128, 4), (3001, 64, 2), (2000, 256, 3), (1500, 1024, 2), (4000, 32, 8),
+                                   (900, 50, 3)])
+def test_lanes_step_equals_separate_steps(N, D, L):
+    """L states with different histories share X: one fused pass must leave every state exactly
+    where its own cs_fps_step leaves it (h bits, voronoi, next key, pick counter), several steps
+    in a row."""
+    dev = torch.device("cuda:0")
+    X = torch.from_numpy(gaussian_mixture(N, D, 8, seed=N + D + L)).to(dev)
+    norms = engine.row_norms(X)
+
+    def make_set():
+        engs = []
+        for l in range(L):
+            e = engine.ShardEngine(X, norms, 64)
+            e.init_state()
+            e.pick_forced((37 * l + 5) % N)
+            e.run_picks(3 * l)                       # lane l has 1 + 3l centres
+            engs.append(e)
+        return engs
+
+    fused, apart = make_set(), make_set()
+    for _ in range(5):
+        for e in fused:
+            e.exchange(); e.commit()
+        engine.ShardEngine.step_lanes(fused)
+        for e in apart:
+            e.exchange(); e.commit(); e.step()
+        for a, b in zip(fused, apart):
+            ca, cb = a.check_status(), b.check_status()
+            assert ca.n_sel == cb.n_sel and list(ca.key) == list(cb.key)
+            assert torch.equal(a.h.view(torch.int32), b.h.view(torch.int32))
+            assert torch.equal(a.voronoi, b.voronoi)
+    for a, b in zip(fused, apart):
+        assert torch.equal(a.selected[: a.check_status().n_sel], b.selected[: b.check_status().n_sel])
