@@ -321,6 +321,46 @@ __global__ void __launch_bounds__(kThreads) commit_bound_kernel(const cs_state s
 // per batch so that RB * CPL 16-byte loads per lane are in flight, every row read with one fully coalesced
 // 512-byte (or wider) request.  CPL = float4 chunks per lane = ceil(D / 128); CPL == 0 is the
 // generic path (any D, centre in shared memory).
+// Rows of at most 64 floats (d4 <= 16) fill only half of a warp-wide request in the reference's lane
+// mapping.  Here the two half-warps take two different rows at once: lanes 0-15 row A, lanes
+// 16-31 row B.  The reference's tree adds p[j+16] (always 0 for such rows) at its first level and
+// then reduces within 16 lanes; the same is done per half-warp, so every bit is kept.
+__device__ __forceinline__ void tile_rows_half(const float4* __restrict__ X4, const int64_t base, const int d4,
+                                               unsigned m, const float4 cen_h, const int lane, float& mydot) {
+    constexpr int PB = kInflight;            // row PAIRS whose loads are in flight together
+    const int sub = lane & 15;
+    const bool hi = lane >= 16;
+    while (m) {
+        int ra[PB], rb[PB];
+        float4 a[PB];
+#pragma unroll
+        for (int b = 0; b < PB; ++b) {
+            ra[b] = m ? (__ffs(m) - 1) : -1;
+            m &= m - 1;
+            rb[b] = m ? (__ffs(m) - 1) : -1;
+            m &= m - 1;
+        }
+#pragma unroll
+        for (int b = 0; b < PB; ++b) {
+            const int r = hi ? rb[b] : ra[b];
+            if (r >= 0 && sub < d4) a[b] = ld_stream4(X4 + (base + (int64_t)r * kRowsPerLane) * (int64_t)d4 + sub);
+        }
+#pragma unroll
+        for (int b = 0; b < PB; ++b) {
+            if (ra[b] < 0) continue;                       // warp-uniform
+            const int r = hi ? rb[b] : ra[b];
+            float p = 0.0f;
+            if (r >= 0 && sub < d4) p = __fadd_rn(p, chunk_dot(a[b], cen_h));
+            p = __fadd_rn(p, 0.0f);                        // level 16 of the tree: the partner lane holds 0
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) p = __fadd_rn(p, __shfl_xor_sync(kFull, p, off));
+            const float pa = __shfl_sync(kFull, p, 0), pb = __shfl_sync(kFull, p, 16);
+            if (lane == ra[b]) mydot = pa;
+            if (lane == rb[b]) mydot = pb;
+        }
+    }
+}
+
 template <int CPL, bool FULL>
 __device__ __forceinline__ void tile_rows(const float4* __restrict__ X4, const int64_t base,
                                           const int d4, unsigned m, const float4 (&cen)[CPL ? CPL : 1],
@@ -358,7 +398,7 @@ __device__ __forceinline__ void tile_rows(const float4* __restrict__ X4, const i
     }
 }
 
-template <int CPL, bool FULL>
+template <int CPL, bool FULL, bool HALF>
 __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const cs_state s, const unsigned mode,
                                                                            const int n_bound_smem) {
     // dynamic shared memory: the first n_bound_smem triangle bounds (the per-row bound lookup is
@@ -394,6 +434,8 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
     } else {
         for (int c = threadIdx.x; c < D; c += blockDim.x) s_cen[c] = cen_g[c];
     }
+    float4 cen_h = make_float4(0.f, 0.f, 0.f, 0.f);      // half-warp mapping: chunk (lane & 15)
+    if (HALF && (lane & 15) < d4) cen_h = reinterpret_cast<const float4*>(cen_g)[lane & 15];
     const int nb = i < n_bound_smem ? i : n_bound_smem;
     for (int c = threadIdx.x; c < nb; c += blockDim.x) s_dsl[c] = s.dSL_quarter[c];
     __syncthreads();
@@ -472,7 +514,8 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
             live_cnt += __popc(mj);
             float dj = 0.0f;
             if (CPL) {
-                tile_rows<CPL, FULL>(X4, base + j, d4, mj, cen, lane, dj);
+                if (HALF) tile_rows_half(X4, base + j, d4, mj, cen_h, lane, dj);
+                else tile_rows<CPL, FULL>(X4, base + j, d4, mj, cen, lane, dj);
             } else {
                 unsigned mm = mj;
                 while (mm) {
@@ -828,14 +871,14 @@ int validate(const cs_state* s) {
 
 constexpr int kBoundSmemMax = 16384;     // triangle bounds staged in shared memory (64 KB)
 
-template <int CPL, bool FULL>
+template <int CPL, bool FULL, bool HALF = false>
 int launch_step(const cs_state* s, unsigned mode, cudaStream_t st, int sms) {
     static thread_local size_t attr_set = 0, occ_smem = ~(size_t)0;
     static thread_local int occ_blocks = 0;
     const int n_bound = (int)(s->cap < kBoundSmemMax ? s->cap : kBoundSmemMax);
     const size_t smem = (size_t)n_bound * sizeof(float) + (CPL ? 0 : (size_t)s->D * sizeof(float));
     if (smem > 48 * 1024 && smem > attr_set) {
-        if (cudaFuncSetAttribute(fps_step_kernel<CPL, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(fps_step_kernel<CPL, FULL, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) {
             g_last_cuda = cudaGetLastError();
             return CS_E_LAUNCH;
@@ -844,7 +887,7 @@ int launch_step(const cs_state* s, unsigned mode, cudaStream_t st, int sms) {
     }
     if (occ_smem != smem) {
         int per_sm = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fps_step_kernel<CPL, FULL>, kThreads, smem) !=
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fps_step_kernel<CPL, FULL, HALF>, kThreads, smem) !=
                 cudaSuccess || per_sm < 1) {
             g_last_cuda = cudaGetLastError();
             return CS_E_LAUNCH;
@@ -856,7 +899,7 @@ int launch_step(const cs_state* s, unsigned mode, cudaStream_t st, int sms) {
     int64_t want = (tiles + kWarps - 1) / kWarps;
     int64_t cap = (int64_t)sms * occ_blocks;     // persistent grid: a multiple of the SM count
     int grid = (int)(want < 1 ? 1 : (want < cap ? want : cap));
-    fps_step_kernel<CPL, FULL><<<grid, kThreads, smem, st>>>(*s, mode, n_bound);
+    fps_step_kernel<CPL, FULL, HALF><<<grid, kThreads, smem, st>>>(*s, mode, n_bound);
     return check_launch();
 }
 
@@ -995,6 +1038,7 @@ int cs_fps_step(const cs_state* s, uint32_t mode, cs_stream stream) {
         case 1024: return launch_step<8, true>(s, mode, st, d.sms);
         default: break;
     }
+    if (D <= 64) return launch_step<1, false, true>(s, mode, st, d.sms);    // two rows per warp-wide load
     if (D < 128) return launch_step<1, false>(s, mode, st, d.sms);
     if (D < 256) return launch_step<2, false>(s, mode, st, d.sms);
     if (D < 512) return launch_step<4, false>(s, mode, st, d.sms);
