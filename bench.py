@@ -411,8 +411,8 @@ def run_e2e(args, X, w, world, rank, device, K, W, off):
     nbytes = n_local * dim * 4
     avail = host_memory_available()
     share = max(1, min(world, torch.cuda.device_count()))
-    # all ranks of this node together must leave a fifth of the host memory (and 24 GiB) free
-    ok = torch.tensor([1 if (nbytes + (4 << 30)) * share + (24 << 30) < 0.8 * avail else 0], device=device)
+    # all ranks of this node together (rows + two 1 GiB staging buffers each) must leave 16 GiB free
+    ok = torch.tensor([1 if (nbytes + (2 << 30)) * share + (16 << 30) < avail else 0], device=device)
     if world > 1:
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if int(ok.item()) == 0:
