@@ -211,6 +211,42 @@ def accrete_goldens(coresets, dev, out, compare):
                   f"engine_accrete_s={t_mine:.2f} reference_accrete_s={t_single:.2f}", flush=True)
 
 
+def midsize_accrete_compare(coresets, dev, out):
+    """Reference vs engine accretion on a larger device-generated matrix (no fixture: evidence of
+    identical lists and the wall time of both)."""
+    import json
+    import time
+    import coresets_b200
+    from coresets_b200.synth import Workload, MixtureSource
+    results = []
+    for n_anchor, n_cand, dim, max_k in ((400_000, 400_000, 64, 11), (1_000_000, 1_000_000, 128, 10)):
+        wa = Workload("acc_anchor", n_anchor, dim, 32, 11, 0)
+        wc = Workload("acc_cand", n_cand, dim, 48, 12, 0, mean_scale=6.0)
+        X = torch.cat([MixtureSource(wa).rows(0, n_anchor, dev), MixtureSource(wc).rows(0, n_cand, dev)])
+        order = coresets_b200.fps_cuda(X[:n_anchor].contiguous(), 2 ** max_k)
+        rec = dict(n_anchor=n_anchor, n_cand=n_cand, dim=dim, max_k=max_k)
+        for tag, env in (("plain", {}), ("knobs", {"CORESETS_BISECT_SEED": "1", "CORESETS_FILL_CHUNK": "256"})):
+            for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK"):
+                os.environ.pop(k, None)
+            os.environ.update(env)
+            torch.cuda.synchronize(); t0 = time.time()
+            ref = coresets.accrete_sharded(X, order, n_anchor, max_k=max_k, verbose=False)
+            torch.cuda.synchronize(); t_ref = time.time() - t0
+            t0 = time.time()
+            mine = coresets_b200.accrete_sharded(X, order, n_anchor, max_k=max_k, verbose=False)
+            torch.cuda.synchronize(); t_new = time.time() - t0
+            rec[f"{tag}_identical"] = bool(torch.equal(ref, mine))
+            rec[f"{tag}_reference_s"] = round(t_ref, 2)
+            rec[f"{tag}_engine_s"] = round(t_new, 2)
+        for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK"):
+            os.environ.pop(k, None)
+        print("[midsize-accrete]", json.dumps(rec), flush=True)
+        results.append(rec)
+        del X
+        torch.cuda.empty_cache()
+    (out / "midsize_accrete_compare.json").write_text(json.dumps(results, indent=1))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=str(ROOT / "gpurun_out" / "golden"))
@@ -246,6 +282,7 @@ def main() -> None:
             compare_with_engine(name, X, K, seeds, sel_api, eps, h, v)
     accrete_goldens(coresets, dev, out, a.compare)
     if a.compare:
+        midsize_accrete_compare(coresets, dev, out)
         midsize_compare(coresets, dev, out)
     dist.destroy_process_group()
 

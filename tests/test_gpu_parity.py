@@ -390,3 +390,12 @@ def test_lanes_step_equals_separate_steps(N, D, L):
             assert torch.equal(a.voronoi, b.voronoi)
     for a, b in zip(fused, apart):
         assert torch.equal(a.selected[: a.check_status().n_sel], b.selected[: b.check_status().n_sel])
+
+
+def test_more_centres_than_the_shared_bound_table():
+    """k above 16384: the bound table no longer fits the 64 KB shared-memory stage, the tail of
+    the look-ups goes to global memory; picks must stay the oracle's."""
+    N, D, k = 30000, 8, 17000
+    X = gaussian_mixture(N, D, 8, seed=77)
+    eng, norms = run_engine(X, k)
+    assert_matches_oracle(eng, X, norms, k)
