@@ -1,6 +1,6 @@
 """Golden vectors for the accretion drivers, produced by the REFERENCE's own Python drivers.
 
-    python tests/golden/make_golden_accrete_cpu.py [--reference /root/reference]
+    python tests/golden/make_golden_accrete_cpu.py --reference <reference checkout>
 
 The reference's `accrete` (src/coresets/cuda/accrete.py) and `accrete_voronoi_multi_sharded`
 (src/coresets/cuda/multi/sharded.py) are run on CPU tensors with the oracle standing in for their
@@ -105,7 +105,7 @@ def worker(ref_root: str, out_dir: str):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("CORESETS_REFERENCE_ROOT", "/root/reference"))
     ap.add_argument("--worker-out", default=None)
     a = ap.parse_args()
     if a.worker_out:

@@ -1,6 +1,6 @@
 """Golden vectors of the reference's CPU backend: run where the reference checkout is importable.
 
-    python tests/golden/make_golden_cpu.py [--reference /root/reference]
+    python tests/golden/make_golden_cpu.py --reference <reference checkout>
 
 Writes tests/golden/cpu_fps_c1.npz: outputs of the reference's own ``coresets.fps``
 (src/coresets/pytorch/fps.py:32-73) on the 20 000 x 64, 16-component, k = 512 case.  Inputs are
@@ -9,6 +9,7 @@ independent of the thread count for this shape, the test checks `selected` exact
 radii to 1e-6 relative).
 """
 import argparse
+import os
 import sys
 from pathlib import Path
 
@@ -20,7 +21,7 @@ sys.path.insert(0, str(ROOT))
 from tests.data import gaussian_mixture  # noqa: E402
 
 ap = argparse.ArgumentParser()
-ap.add_argument("--reference", default="/root/reference")
+ap.add_argument("--reference", default=os.environ.get("CORESETS_REFERENCE_ROOT", "/root/reference"))
 a = ap.parse_args()
 sys.path.insert(0, str(Path(a.reference) / "src"))
 from coresets import fps  # noqa: E402

@@ -4,7 +4,7 @@ Needs (all git-ignored, produced on a machine that has the reference checkout):
   oracle/_ref/site/   `pip install --no-deps --target oracle/_ref/site <reference checkout>`
   oracle/_ref/build/  `python oracle/build_ref.py` (the reference's kernels, its own flags)
 
-Run on a B200:   python tests/golden/make_golden_gpu.py --out gpurun_out/golden
+Run on a B200:   python tests/golden/make_golden_gpu.py --out <output directory>
 then copy the produced *.npz next to this file.  Each file holds the inputs that cannot be
 regenerated bit-exactly elsewhere (the float32 row norms torch computed on the GPU) and the
 reference's outputs: `selected` from its public `fps_cuda`, `selected`/`epsilons` from its
@@ -249,7 +249,7 @@ def midsize_accrete_compare(coresets, dev, out):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default=str(ROOT / "gpurun_out" / "golden"))
+    ap.add_argument("--out", default=str(ROOT / "golden_out"))
     ap.add_argument("--compare", action="store_true", help="also run this repository's engine side by side")
     a = ap.parse_args()
     out = Path(a.out)

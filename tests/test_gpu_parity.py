@@ -209,7 +209,7 @@ def test_multi_rank_kernels_on_one_device(sizes):
 
 
 def test_large_shard_properties():
-    """BASELINE-sized shard (the 8-GPU share of the 300M x 128 config: 37.5M rows, 19.2 GB)
+    """Benchmark-sized shard (the 8-GPU share of the 300M x 128 config: 37.5M rows, 19.2 GB)
     checked through size-independent properties: unique picks, non-increasing radii, dense and
     prune modes agreeing, and for sampled rows h == distance to the centre voronoi names, bitwise
     in the reference's arithmetic."""
