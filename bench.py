@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument("--workload", default="c3")
     ap.add_argument("--rows", type=int, default=0, help="override the workload's global row count")
     ap.add_argument("--prune-picks", type=int, default=384, help="picks run before the prune-mode timing")
+    ap.add_argument("--dense-kernel", default="tma", choices=["tma", "ldg"],
+                    help="dense mode: X through the TMA ring (default) or plain 128-bit loads")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prune", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -186,7 +188,7 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------- GPU arm
 def run_ours(args):
     from coresets_b200 import _native, engine
-    from coresets_b200._native import MODE_DENSE, MODE_PRUNE
+    from coresets_b200._native import MODE_DENSE, MODE_DENSE_LDG, MODE_PRUNE
     from coresets_b200.cuda.multi.layout import compute_shard_layout
     from coresets_b200.synth import WORKLOADS, MixtureSource, scaled
 
@@ -225,7 +227,8 @@ def run_ours(args):
     torch.cuda.synchronize(device)
     t_gen = time.time() - t_gen
 
-    eng = engine.ShardEngine(X, norms, cap, shard_offset=off, world_size=world, mode=MODE_DENSE)
+    dense_mode = MODE_DENSE if args.dense_kernel == "tma" else MODE_DENSE_LDG
+    eng = engine.ShardEngine(X, norms, cap, shard_offset=off, world_size=world, mode=dense_mode)
     eng.init_state()
     eng.pick_forced(0)
     eng.prepare(max(W, 1))
@@ -325,7 +328,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "traffic": traffic,
                          "traffic_source": "ncu dram__bytes_read+write on 8M x 128 (525.3 B/row), scaled by rows",
-                         "kernel": "fps_step_kernel (dense)",
+                         "kernel": "fps_step_tma_kernel (dense, cp.async.bulk ring)" if args.dense_kernel == "tma" else "fps_step_kernel (dense, LDG.128)",
                          "kernel_ms": kern_ms, "algorithmic_bytes_per_launch": algo_bytes,
                          "live_rows_last_launch_rank0": int(live_dense)},
             "step_breakdown_ms": {"fps_step": kern_ms, "commit_bound": statistics.mean(commit_ms),

@@ -35,7 +35,7 @@ struct Ctl {
 static_assert(sizeof(Ctl) <= CS_CTL_BYTES, "control block too large");
 static_assert(sizeof(cs_ctl_view) == CS_CTL_BYTES, "cs_ctl_view must span the control block");
 
-enum { ST_CAPACITY = 1, ST_FORCE_NOT_OWNED = 2, ST_XCHG_TIMEOUT = 3 };
+enum { ST_CAPACITY = 1, ST_FORCE_NOT_OWNED = 2, ST_XCHG_TIMEOUT = 3, ST_PIPE_TIMEOUT = 4 };
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
@@ -583,6 +583,298 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
     }
 }
 
+// ---- dense mode through the TMA engine -------------------------------------------------------------
+// Every live row is read in dense mode, so X can be streamed by bulk asynchronous copies
+// (cp.async.bulk, the 1-D TMA path: rows are contiguous, no tensor map needed) into a ring of
+// shared-memory stages, with the copies of several stages in flight while the consumer warps work:
+// memory-level parallelism no longer depends on registers or occupancy.  One producer warp issues
+// the copies and arms the "full" mbarriers with the byte count; eight consumer warps wait on
+// "full", take their rows of the tile from shared memory (512-byte conflict-free reads), run the
+// same per-row arithmetic as fps_step_kernel, and release the stage through the "empty" mbarrier.
+// Every wait is bounded; a wait that runs out sets status = 4 and the block drains and leaves.
+// Ring shapes per row width, found by measurement on B200 (stages S, resident blocks per SM B,
+// bytes of X per stage T, consumer warps W): one block per SM with 160-200 KB of copies in flight;
+// narrow rows need sixteen consumer warps to keep up with the ring.
+#ifndef CS_TMA_NARROW_S
+#define CS_TMA_NARROW_S 3
+#endif
+#ifndef CS_TMA_NARROW_B
+#define CS_TMA_NARROW_B 1
+#endif
+#ifndef CS_TMA_NARROW_T
+#define CS_TMA_NARROW_T 65536
+#endif
+#ifndef CS_TMA_NARROW_W
+#define CS_TMA_NARROW_W 16
+#endif
+#ifndef CS_TMA_MID_S
+#define CS_TMA_MID_S 3
+#endif
+#ifndef CS_TMA_MID_B
+#define CS_TMA_MID_B 1
+#endif
+#ifndef CS_TMA_MID_T
+#define CS_TMA_MID_T 65536
+#endif
+#ifndef CS_TMA_MID_W
+#define CS_TMA_MID_W 8
+#endif
+#ifndef CS_TMA_WIDE_S
+#define CS_TMA_WIDE_S 5
+#endif
+#ifndef CS_TMA_WIDE_B
+#define CS_TMA_WIDE_B 1
+#endif
+#ifndef CS_TMA_WIDE_T
+#define CS_TMA_WIDE_T 40960
+#endif
+#ifndef CS_TMA_WIDE_W
+#define CS_TMA_WIDE_W 8
+#endif
+struct RingCfg { int stages, blocks, tile_bytes, warps; };
+constexpr RingCfg kRingNarrow{CS_TMA_NARROW_S, CS_TMA_NARROW_B, CS_TMA_NARROW_T, CS_TMA_NARROW_W};   // D <= 64
+constexpr RingCfg kRingMid{CS_TMA_MID_S, CS_TMA_MID_B, CS_TMA_MID_T, CS_TMA_MID_W};                  // 64 < D <= 128
+constexpr RingCfg kRingWide{CS_TMA_WIDE_S, CS_TMA_WIDE_B, CS_TMA_WIDE_T, CS_TMA_WIDE_W};             // 128 < D <= 1024
+constexpr int kTmaMaxWarps = 16;
+constexpr int kSpinLimit = 1 << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* b, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity) {
+    for (int it = 0; it < kSpinLimit; ++it) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* b) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(b)) : "memory");
+}
+
+template <int CPL, int S, bool HALF, int W, int B>
+__global__ void __launch_bounds__((W + 1) * 32, B) fps_step_tma_kernel(const cs_state s, const int tile_rows) {
+    // S stages; a stage holds the tile's rows of X, then their h, voronoi and norm words
+    extern __shared__ __align__(128) unsigned char s_tile[];
+    __shared__ uint64_t s_full[S], s_empty[S];
+    __shared__ u64 s_keys[W];
+    __shared__ unsigned s_live[W];
+    __shared__ int s_last, s_abort;
+
+    Ctl* ctl = reinterpret_cast<Ctl*>(s.ctl);
+    const int i = ctl->n_sel;
+    if (i >= s.cap) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) ctl->status = ST_CAPACITY;
+        return;
+    }
+    const int D = s.D, d4 = D >> 2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool first = (i == 0);
+    const float nn = s.norms_sel[i];
+    const int64_t N = s.N_local;
+    const int n32 = (int)N;
+    const int x_bytes = tile_rows * D * 4;
+    const int stage_bytes = x_bytes + 3 * tile_rows * 4;
+    const int ntiles = (int)((N + tile_rows - 1) / tile_rows);
+    const int rpw = tile_rows / W;                           // rows of a tile per consumer warp (<= 32)
+
+    if (threadIdx.x == 0) {
+        for (int q = 0; q < S; ++q) { mbar_init(&s_full[q], 1); mbar_init(&s_empty[q], W); }
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    float best_h = __uint_as_float(0xff800000u);
+    int best_row = -1;
+    unsigned live_cnt = 0;
+
+    if (warp == W) {
+        // ---- producer: keep S tiles in flight -----------------------------------------------------
+        if (lane == 0) {
+            int n = 0;
+            for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++n) {
+                const int q = n % S;
+                if (n >= S && !mbar_wait(&s_empty[q], (uint32_t)((n / S) - 1) & 1u)) {
+                    ctl->status = ST_PIPE_TIMEOUT;
+                    s_abort = 1;
+                    break;
+                }
+                if (*(volatile int*)&s_abort) break;
+                const int64_t row0 = (int64_t)t * tile_rows;
+                const int rows = (int)((N - row0) < tile_rows ? (N - row0) : tile_rows);
+                const int rows4 = rows & ~3;                       // a bulk copy moves multiples of 16 bytes
+                unsigned char* st = s_tile + (size_t)q * stage_bytes;
+                float* sh = reinterpret_cast<float*>(st + x_bytes);
+                int* sv = reinterpret_cast<int*>(sh + tile_rows);
+                float* sn = sh + 2 * tile_rows;
+                for (int r = rows4; r < rows; ++r) {               // the last tile's odd rows, by plain loads
+                    sh[r] = s.h[row0 + r];
+                    sv[r] = s.voronoi[row0 + r];
+                    sn[r] = s.norms[row0 + r];
+                }
+                const uint32_t xb = (uint32_t)rows * (uint32_t)D * 4u, mb = (uint32_t)rows4 * 4u;
+                mbar_expect_tx(&s_full[q], xb + 3u * mb);          // release: the plain stores above are visible
+                bulk_load(st, s.X + row0 * (int64_t)D, xb, &s_full[q]);
+                if (mb) {
+                    bulk_load(sh, s.h + row0, mb, &s_full[q]);
+                    bulk_load(sv, s.voronoi + row0, mb, &s_full[q]);
+                    bulk_load(sn, s.norms + row0, mb, &s_full[q]);
+                }
+            }
+        }
+    } else {
+        // ---- consumers ------------------------------------------------------------------------------
+        const int sub = HALF ? (lane & 15) : lane;
+        const bool hi = HALF && lane >= 16;
+        float4 cen[CPL];
+        {
+            const float4* c4 = reinterpret_cast<const float4*>(s.X_sel + (int64_t)i * D);
+#pragma unroll
+            for (int c = 0; c < CPL; ++c)
+                cen[c] = (sub + 32 * c < d4) ? c4[sub + 32 * c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        int n = 0;
+        for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++n) {
+            const int q = n % S;
+            if (!__all_sync(kFull, mbar_wait(&s_full[q], (uint32_t)(n / S) & 1u))) {   // warp-uniform verdict
+                if (lane == 0) { ctl->status = ST_PIPE_TIMEOUT; s_abort = 1; }
+                break;
+            }
+            const unsigned char* st = s_tile + (size_t)q * stage_bytes;
+            const float* sh = reinterpret_cast<const float*>(st + x_bytes);
+            const int* sv = reinterpret_cast<const int*>(sh + tile_rows);
+            const float* sn = sh + 2 * tile_rows;
+            // lane j < rpw owns row (t * tile_rows + warp * rpw + j)
+            const int slot_row = warp * rpw + lane;
+            const int row = t * tile_rows + slot_row;
+            const bool valid = lane < rpw && row < n32;
+            float hq = valid ? sh[slot_row] : __uint_as_float(0xff800000u);
+            const bool live = !(hq < 0.0f) && valid;                          // warp.cu:28-30, 75-77
+            float bound = 0.0f, nrow = 0.0f;
+            if (live) {
+                if (!first) bound = __ldg(s.dSL_quarter + sv[slot_row]);      // used after the dot products
+                nrow = sn[slot_row];
+            }
+            unsigned m = __ballot_sync(kFull, live);
+            live_cnt += __popc(m);
+            const float4* tile4 = reinterpret_cast<const float4*>(st) + (warp * rpw) * d4;
+            float mydot = 0.0f;
+            // Rows are taken in batches whose arithmetic is free of branches, so that the shuffle
+            // chains of a batch overlap: an empty slot of the last batch re-reads row 0 and its sum
+            // is dropped (no lane equals -1).
+            if (HALF) {
+                constexpr int PB = 4;                                          // row pairs per batch
+                while (m) {
+                    int ra[PB], rb[PB];
+                    float4 a[PB];
+#pragma unroll
+                    for (int b = 0; b < PB; ++b) {
+                        ra[b] = m ? (__ffs(m) - 1) : -1;
+                        m &= m - 1;
+                        rb[b] = m ? (__ffs(m) - 1) : -1;
+                        m &= m - 1;
+                    }
+#pragma unroll
+                    for (int b = 0; b < PB; ++b) {
+                        const int r = hi ? rb[b] : ra[b];
+                        a[b] = tile4[(r < 0 ? 0 : r) * d4 + (sub < d4 ? sub : 0)];
+                    }
+#pragma unroll
+                    for (int b = 0; b < PB; ++b) {
+                        float p = 0.0f;
+                        if (sub < d4) p = __fadd_rn(p, chunk_dot(a[b], cen[0]));
+                        p = __fadd_rn(p, 0.0f);                                // level 16 of the tree: the partner holds 0
+#pragma unroll
+                        for (int off = 8; off > 0; off >>= 1) p = __fadd_rn(p, __shfl_xor_sync(kFull, p, off));
+                        const float pa = __shfl_sync(kFull, p, 0), pb = __shfl_sync(kFull, p, 16);
+                        if (lane == ra[b]) mydot = pa;
+                        if (lane == rb[b]) mydot = pb;
+                    }
+                }
+            } else {
+                constexpr int RBS = CPL >= 8 ? 1 : 8 / CPL;                    // rows read from the stage together
+                while (m) {
+                    int rows[RBS];
+                    float4 a[RBS][CPL];
+#pragma unroll
+                    for (int b = 0; b < RBS; ++b) {
+                        rows[b] = m ? (__ffs(m) - 1) : -1;
+                        m &= m - 1;
+                    }
+#pragma unroll
+                    for (int b = 0; b < RBS; ++b) {
+                        const int r = rows[b] < 0 ? 0 : rows[b];
+#pragma unroll
+                        for (int c = 0; c < CPL; ++c)
+                            a[b][c] = tile4[r * d4 + (lane + 32 * c < d4 ? lane + 32 * c : 0)];
+                    }
+#pragma unroll
+                    for (int b = 0; b < RBS; ++b) {
+                        float p = 0.0f;
+#pragma unroll
+                        for (int c = 0; c < CPL; ++c)
+                            if (lane + 32 * c < d4) p = __fadd_rn(p, chunk_dot(a[b][c], cen[c]));
+                        p = warp_tree_sum(p);
+                        if (lane == rows[b]) mydot = p;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[q]);                        // the stage may be refilled
+            if (live && (first || !(bound >= hq))) {                        // warp.cu:80-82
+                const float d = sq_dist(nrow, nn, mydot);
+                if (d < hq) {
+                    hq = d;
+                    s.h[row] = d;
+                    s.voronoi[row] = i;
+                }
+            }
+            if (hq > best_h) { best_h = hq; best_row = row; }               // rows come in order per lane
+        }
+    }
+
+    u64 best = best_row >= 0 ? make_key(best_h, s.shard_offset + best_row) : 0;
+    best = warp_max_key(best);
+    if (lane == 0 && warp < W) { s_keys[warp] = best; s_live[warp] = live_cnt; }
+    __syncthreads();
+    if (s_abort && warp == W && lane == 0) {
+        // a wait ran out: let copies that may still be in flight land before the block's shared
+        // memory is released (bounded)
+        for (int q = 0; q < S; ++q) { (void)mbar_wait(&s_full[q], 0u); (void)mbar_wait(&s_full[q], 1u); }
+    }
+    const int slot = (i + 1) & 1;
+    if (threadIdx.x == 0) {
+        u64 bk = 0;
+        unsigned lv = 0;
+#pragma unroll
+        for (int w = 0; w < W; ++w) { bk = s_keys[w] > bk ? s_keys[w] : bk; lv += s_live[w]; }
+        if (bk) atomicMax(&ctl->key[slot], bk);
+        if (lv) atomicAdd(&ctl->live_rows, (u64)lv);
+        __threadfence();
+        s_last = (atomicAdd(&ctl->ticket, 1u) == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const u64 k = *reinterpret_cast<volatile u64*>(&ctl->key[slot]);
+    if (s.world_size > 1) publish_candidate(s, ctl, k, key_idx(k) - s.shard_offset);
+    if (threadIdx.x == 0) {
+        ctl->ticket = 0;
+        ctl->n_sel = i + 1;
+    }
+}
+
 // ---- several probes in one pass over X ("lanes") ------------------------------------------------
 // L independent states (own h, voronoi, centre table, control block) share X and norms.  A warp
 // owns tiles of 32 consecutive rows; lane j of the warp holds, for every state, h / voronoi of row
@@ -869,6 +1161,31 @@ int validate(const cs_state* s) {
     return CS_OK;
 }
 
+template <int CPL, bool HALF, int S, int B, int T, int W>
+int launch_step_tma(const cs_state* s, cudaStream_t st, int sms) {
+    static_assert(W <= kTmaMaxWarps && (W % 8) == 0, "consumer warps");
+    const int D = s->D;
+    int tile_rows = T / (D * 4);
+    tile_rows = tile_rows > 32 * W ? 32 * W : tile_rows;   // a lane owns one row of its warp's share
+    tile_rows -= tile_rows % W;                             // W is a multiple of 8: 16-byte multiples of h / voronoi / norms
+    if (tile_rows < W) tile_rows = W;
+    const size_t smem = (size_t)S * tile_rows * (D * 4 + 12);   // rows of X, then h / voronoi / norm words
+    static thread_local size_t attr_set = 0;
+    if (smem > attr_set) {
+        if (cudaFuncSetAttribute(fps_step_tma_kernel<CPL, S, HALF, W, B>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess) {
+            g_last_cuda = cudaGetLastError();
+            return CS_E_LAUNCH;
+        }
+        attr_set = smem;
+    }
+    const int64_t ntiles = (s->N_local + tile_rows - 1) / tile_rows;
+    int64_t cap = (int64_t)sms * B;                         // resident blocks, each with its own ring
+    int grid = (int)(ntiles < 1 ? 1 : (ntiles < cap ? ntiles : cap));
+    fps_step_tma_kernel<CPL, S, HALF, W, B><<<grid, (W + 1) * 32, smem, st>>>(*s, tile_rows);
+    return check_launch();
+}
+
 constexpr int kBoundSmemMax = 16384;     // triangle bounds staged in shared memory (64 KB)
 
 template <int CPL, bool FULL, bool HALF = false>
@@ -1025,11 +1342,21 @@ int cs_commit_bound(const cs_state* s, uint32_t rules, cs_stream stream) {
 int cs_fps_step(const cs_state* s, uint32_t mode, cs_stream stream) {
     int rc = validate(s);
     if (rc) return rc;
-    if (mode > CS_MODE_DENSE) return CS_E_ARG;
+    if (mode != CS_MODE_PRUNE && mode != CS_MODE_DENSE && mode != CS_MODE_DENSE_LDG) return CS_E_ARG;
     DevInfo d = device_info();
     if (!d.ok) return CS_E_DEVICE;
     cudaStream_t st = (cudaStream_t)stream;
     const int D = s->D;
+    // dense mode streams X through the TMA ring when rows are whole 16-byte chunks of moderate width
+    // bulk copies need 16-byte aligned sources; anything else takes the plain-load kernel
+    const bool bulk_ok = (((uintptr_t)s->X | (uintptr_t)s->h | (uintptr_t)s->voronoi | (uintptr_t)s->norms) & 15u) == 0;
+    if (mode == CS_MODE_DENSE && bulk_ok && (D & 3) == 0 && D >= 32 && D <= 1024 && s->N_local > 0) {
+        if (D <= 64) return launch_step_tma<1, true, kRingNarrow.stages, kRingNarrow.blocks, kRingNarrow.tile_bytes, kRingNarrow.warps>(s, st, d.sms);
+        if (D <= 128) return launch_step_tma<1, false, kRingMid.stages, kRingMid.blocks, kRingMid.tile_bytes, kRingMid.warps>(s, st, d.sms);
+        if (D <= 256) return launch_step_tma<2, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d.sms);
+        if (D <= 512) return launch_step_tma<4, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d.sms);
+        return launch_step_tma<8, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d.sms);
+    }
     if ((D & 3) != 0 || D > 1024) return launch_step<0, false>(s, mode, st, d.sms);
     switch (D) {
         case 128: return launch_step<1, true>(s, mode, st, d.sms);

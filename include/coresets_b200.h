@@ -51,7 +51,9 @@ extern "C" {
 /* cs_fps_step flags */
 #define CS_MODE_PRUNE 0u   /* rows excluded by the triangle bound are not loaded (default) */
 #define CS_MODE_DENSE 1u   /* every live row's distance is computed; the bound only masks the
-                              update, so results are identical to CS_MODE_PRUNE */
+                              update, so results are identical to CS_MODE_PRUNE; X is streamed by
+                              bulk asynchronous (TMA) copies when D % 4 == 0 and 32 <= D <= 1024 */
+#define CS_MODE_DENSE_LDG 3u /* dense mode with plain 128-bit loads (the path other row widths take) */
 /* cs_commit_bound flags */
 #define CS_RULE_NONE 0u    /* plain FPS: no separation bookkeeping */
 #define CS_RULE_SIM_SINGLE 1u   /* commit_center_with_sep_kernel rules (commit.cu:41-51) */

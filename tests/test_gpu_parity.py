@@ -74,10 +74,24 @@ def test_fps_matches_oracle_prune(N, D, k):
     assert_matches_oracle(eng, X, norms, k)
 
 
-@pytest.mark.parametrize("N,D,k", [(33, 64, 20), (4097, 128, 300), (2500, 256, 100), (800, 50, 64), (900, 1024, 48)])
+DENSE_SHAPES = [(33, 64, 20), (4097, 128, 300), (2500, 256, 100), (800, 50, 64), (900, 1024, 48), (3000, 192, 64),
+                (1200, 100, 64), (1000, 32, 128), (16383, 128, 256), (700, 1028, 40), (5, 128, 5), (20000, 36, 100),
+                (1500, 512, 64), (31, 8, 31), (1002, 64, 40), (258, 48, 30)]
+
+
+@pytest.mark.parametrize("N,D,k", DENSE_SHAPES)
 def test_dense_mode_is_bit_identical(N, D, k):
+    """Dense mode (X streamed through the TMA ring where the row width allows it)."""
     X = gaussian_mixture(N, D, 8, seed=N + D)
     eng, norms = run_engine(X, k, mode=MODE_DENSE)
+    assert_matches_oracle(eng, X, norms, k)
+
+
+@pytest.mark.parametrize("N,D,k", [(4097, 128, 300), (2500, 256, 100), (900, 1024, 48), (20000, 36, 100)])
+def test_dense_mode_with_plain_loads_is_bit_identical(N, D, k):
+    from coresets_b200._native import MODE_DENSE_LDG
+    X = gaussian_mixture(N, D, 8, seed=N + D)
+    eng, norms = run_engine(X, k, mode=MODE_DENSE_LDG)
     assert_matches_oracle(eng, X, norms, k)
 
 
