@@ -273,9 +273,11 @@ def run_ours(args):
     algo_bytes = max(sizes) * (4 * w.dim + 8)                # per launch, the largest shard
     achieved = algo_bytes / (kern_ms / 1e3) / 1e9
     peak, peak_kind = peaks()
-    # DRAM traffic per launch: ncu capture of this kernel on 8M x 128 (profiles/) read 4.1921 GB and
-    # wrote 0.0101 GB for 8e6 rows = 525.3 B per row; traffic is proportional to the rows of a launch
-    traffic = max(sizes) * 525.3 if w.dim == 128 else None
+    # DRAM traffic per launch: ncu captures of the dense kernels on 8M x 128 (profiles/) read 4.192 GB
+    # and wrote 0.023 GB (bulk-copy ring) / 0.010 GB (plain loads) for 8e6 rows = 526.8 / 525.3 B per
+    # row; traffic is proportional to the rows of a launch
+    bytes_per_row = 526.8 if args.dense_kernel == "tma" else 525.3
+    traffic = max(sizes) * bytes_per_row if w.dim == 128 else None
     live_dense = eng.read_ctl().live_rows
 
     # ---- default product mode (triangle-bound skip) -------------------------------------------
@@ -327,7 +329,7 @@ def run_ours(args):
                        "generate_s": round(t_gen, 2), "sms": sms},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "traffic": traffic,
-                         "traffic_source": "ncu dram__bytes_read+write on 8M x 128 (525.3 B/row), scaled by rows",
+                         "traffic_source": f"ncu dram__bytes_read+write on 8M x 128 ({bytes_per_row} B/row), scaled by rows",
                          "kernel": "fps_step_tma_kernel (dense, cp.async.bulk ring)" if args.dense_kernel == "tma" else "fps_step_kernel (dense, LDG.128)",
                          "kernel_ms": kern_ms, "algorithmic_bytes_per_launch": algo_bytes,
                          "live_rows_last_launch_rank0": int(live_dense)},

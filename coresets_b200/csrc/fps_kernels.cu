@@ -699,11 +699,12 @@ __global__ void __launch_bounds__((W + 1) * 32, B) fps_step_tma_kernel(const cs_
     int best_row = -1;
     unsigned live_cnt = 0;
 
+    int issued = 0;                                               // producer: tiles whose copies were started
     if (warp == W) {
         // ---- producer: keep S tiles in flight -----------------------------------------------------
         if (lane == 0) {
             int n = 0;
-            for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++n) {
+            for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++n, issued = n) {
                 const int q = n % S;
                 if (n >= S && !mbar_wait(&s_empty[q], (uint32_t)((n / S) - 1) & 1u)) {
                     ctl->status = ST_PIPE_TIMEOUT;
@@ -849,9 +850,10 @@ __global__ void __launch_bounds__((W + 1) * 32, B) fps_step_tma_kernel(const cs_
     if (lane == 0 && warp < W) { s_keys[warp] = best; s_live[warp] = live_cnt; }
     __syncthreads();
     if (s_abort && warp == W && lane == 0) {
-        // a wait ran out: let copies that may still be in flight land before the block's shared
-        // memory is released (bounded)
-        for (int q = 0; q < S; ++q) { (void)mbar_wait(&s_full[q], 0u); (void)mbar_wait(&s_full[q], 1u); }
+        // a wait ran out: let the copies that may still be in flight land before the block's
+        // shared memory is released (each wait bounded): the last tile started on stage q was
+        // number q + S * floor((issued - 1 - q) / S), whose phase parity is waited for
+        for (int q = 0; q < S && q < issued; ++q) (void)mbar_wait(&s_full[q], (uint32_t)((issued - 1 - q) / S) & 1u);
     }
     const int slot = (i + 1) & 1;
     if (threadIdx.x == 0) {
