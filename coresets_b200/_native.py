@@ -13,7 +13,8 @@ from typing import Optional
 
 from . import build as _build
 
-CS_ABI_VERSION = 3
+CS_ABI_VERSION = 4
+F_ELEMENT_ORDER = 1
 CS_CTL_BYTES = 256
 
 MODE_PRUNE = 0
@@ -57,7 +58,7 @@ class CsState(ctypes.Structure):
         ("xchg", ctypes.c_int32),
         ("peer_win", ctypes.c_void_p * MAX_PEERS),
         ("xchg_timeout_ms", ctypes.c_int32),
-        ("reserved0", ctypes.c_int32),
+        ("flags", ctypes.c_int32),
     ]
 
 

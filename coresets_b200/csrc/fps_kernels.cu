@@ -115,9 +115,10 @@ __device__ __forceinline__ float4 ld_stream4(const float4* p) { return __ldcs(p)
 
 // Generic warp dot: row in global memory, centre anywhere (shared or global); any D.
 __device__ __forceinline__ float warp_dot_generic(const float* __restrict__ row,
-                                                  const float* __restrict__ cen, int D, int lane) {
+                                                  const float* __restrict__ cen, int D, int lane,
+                                                  bool element_order) {
     float acc = 0.0f;
-    if ((D & 3) == 0) {
+    if ((D & 3) == 0 && !element_order) {
         const float4* r4 = reinterpret_cast<const float4*>(row);
         const float4* c4 = reinterpret_cast<const float4*>(cen);
         const int d4 = D >> 2;
@@ -310,7 +311,7 @@ __global__ void __launch_bounds__(kThreads) commit_bound_kernel(const cs_state s
     const int gw = blockIdx.x * kWarps + (threadIdx.x >> 5);
     const int nw = gridDim.x * kWarps;
     for (int v = gw; v < i; v += nw) {
-        float dot = warp_dot_generic(s.X_sel + (int64_t)v * D, s_cen, D, lane);
+        float dot = warp_dot_generic(s.X_sel + (int64_t)v * D, s_cen, D, lane, (s.flags & CS_F_ELEMENT_ORDER) != 0);
         if (lane == 0) s.dSL_quarter[v] = __fmul_rn(sq_dist(s.norms_sel[v], w.norm, dot), 0.25f);
     }
 }
@@ -417,6 +418,7 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
         return;
     }
     const int D = s.D;
+    const bool element_order = (s.flags & CS_F_ELEMENT_ORDER) != 0;   // generic path only
     const int d4 = D >> 2;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -521,7 +523,7 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
                 while (mm) {
                     const int r = __ffs(mm) - 1;
                     mm &= mm - 1;
-                    float p = warp_dot_generic(s.X + (base + j + (int64_t)r * kRowsPerLane) * (int64_t)D, s_cen, D, lane);
+                    float p = warp_dot_generic(s.X + (base + j + (int64_t)r * kRowsPerLane) * (int64_t)D, s_cen, D, lane, element_order);
                     if (lane == r) dj = p;
                 }
             }
@@ -1352,14 +1354,15 @@ int cs_fps_step(const cs_state* s, uint32_t mode, cs_stream stream) {
     // dense mode streams X through the TMA ring when rows are whole 16-byte chunks of moderate width
     // bulk copies need 16-byte aligned sources; anything else takes the plain-load kernel
     const bool bulk_ok = (((uintptr_t)s->X | (uintptr_t)s->h | (uintptr_t)s->voronoi | (uintptr_t)s->norms) & 15u) == 0;
-    if (mode == CS_MODE_DENSE && bulk_ok && (D & 3) == 0 && D >= 32 && D <= 1024 && s->N_local > 0) {
+    const bool element_order = (s->flags & CS_F_ELEMENT_ORDER) != 0;
+    if (mode == CS_MODE_DENSE && bulk_ok && !element_order && (D & 3) == 0 && D >= 32 && D <= 1024 && s->N_local > 0) {
         if (D <= 64) return launch_step_tma<1, true, kRingNarrow.stages, kRingNarrow.blocks, kRingNarrow.tile_bytes, kRingNarrow.warps>(s, st, d.sms);
         if (D <= 128) return launch_step_tma<1, false, kRingMid.stages, kRingMid.blocks, kRingMid.tile_bytes, kRingMid.warps>(s, st, d.sms);
         if (D <= 256) return launch_step_tma<2, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d.sms);
         if (D <= 512) return launch_step_tma<4, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d.sms);
         return launch_step_tma<8, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d.sms);
     }
-    if ((D & 3) != 0 || D > 1024) return launch_step<0, false>(s, mode, st, d.sms);
+    if (element_order || (D & 3) != 0 || D > 1024) return launch_step<0, false>(s, mode, st, d.sms);
     switch (D) {
         case 128: return launch_step<1, true>(s, mode, st, d.sms);
         case 256: return launch_step<2, true>(s, mode, st, d.sms);
@@ -1422,12 +1425,12 @@ int cs_fps_step_lanes(const cs_state* lanes, int32_t n_lanes, uint32_t mode, cs_
         int rc = validate(&lanes[l]);
         if (rc) return rc;
         if (lanes[l].X != lanes[0].X || lanes[l].norms != lanes[0].norms || lanes[l].N_local != lanes[0].N_local ||
-            lanes[l].D != lanes[0].D || lanes[l].shard_offset != lanes[0].shard_offset)
+            lanes[l].D != lanes[0].D || lanes[l].shard_offset != lanes[0].shard_offset || lanes[l].flags != lanes[0].flags)
             return CS_E_ARG;                   // lanes share the matrix; only their state differs
     }
     const int D = lanes[0].D;
     // one lane, rows that are not 16-byte chunks, or very wide rows: the single-state kernel per lane
-    if (n_lanes == 1 || (D & 3) != 0 || D > 1024 || lanes[0].N_local == 0) {
+    if (n_lanes == 1 || (lanes[0].flags & CS_F_ELEMENT_ORDER) || (D & 3) != 0 || D > 1024 || lanes[0].N_local == 0) {
         for (int l = 0; l < n_lanes; ++l) {
             int rc = cs_fps_step(&lanes[l], mode, stream);
             if (rc) return rc;
@@ -1542,7 +1545,7 @@ extern "C" int cs_fps_step_noalloc(const float* X, const float* norms, float* h,
     s.rank = 0;
     s.xchg = CS_XCHG_GATHER;
     s.xchg_timeout_ms = 0;
-    s.reserved0 = 0;
+    s.flags = 0;
     for (int r = 0; r < CS_MAX_PEERS; ++r) s.peer_win[r] = nullptr;
 
     noalloc_prepare_kernel<<<1, 256, 0, st>>>(scratch, centre, norm_new, D, sel_pos);

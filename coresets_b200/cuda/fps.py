@@ -37,8 +37,8 @@ def fps(
     n_total, dim = X.shape
     if not 1 <= n_to_select <= n_total:
         raise ValueError(f"n_to_select={n_to_select} must be in [1, N={n_total}]")
-    if X.dtype != torch.float32:
-        raise ValueError(f"fps_cuda computes in float32; got X.dtype={X.dtype}")
+    if X.dtype not in (torch.float32, torch.float64, torch.float16):
+        raise ValueError(f"X must be float32, float64 or float16, got X.dtype={X.dtype}")
 
     if seed is not None:
         if seed.dim() != 1:
@@ -54,8 +54,9 @@ def fps(
         seed_list = [0]
 
     X = X.contiguous()
-    norms = _engine.row_norms(X)
-    eng = _engine.ShardEngine(X, norms, n_to_select)
+    norms = _engine.row_norms(X)                       # in X's own dtype, as fps.py:34 does
+    X32, element_order = _engine.engine_matrix(X)
+    eng = _engine.ShardEngine(X32, norms, n_to_select, element_order=element_order)
     eng.init_state()
     for idx in seed_list:
         eng.pick_forced(idx)

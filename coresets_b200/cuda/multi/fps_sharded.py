@@ -91,14 +91,15 @@ def fps_sharded(
             f"D={dim} disagrees with peers (cluster min={d_min}, max={d_max}). "
             "Every rank must hold the same feature dim."
         )
-    if X_local.dtype != torch.float32:
-        raise ValueError(f"fps_sharded computes in float32; got X_local.dtype={X_local.dtype}")
+    if X_local.dtype not in (torch.float32, torch.float64, torch.float16):
+        raise ValueError(f"X_local must be float32, float64 or float16, got X_local.dtype={X_local.dtype}")
 
     X_local = X_local.contiguous()
-    norms_local = _engine.row_norms(X_local)
+    norms_local = _engine.row_norms(X_local)           # in X's own dtype, as fps_sharded.py:90 does
+    X32, element_order = _engine.engine_matrix(X_local)
     eng = _engine.ShardEngine(
-        X_local, norms_local, n_to_select, shard_offset=layout.shard_offset,
-        world_size=world_size, group=None,
+        X32, norms_local, n_to_select, shard_offset=layout.shard_offset,
+        world_size=world_size, group=None, element_order=element_order,
     )
     eng.init_state()
 

@@ -43,6 +43,30 @@ def row_norms(X: torch.Tensor) -> torch.Tensor:
     return out
 
 
+_CONVERT_CHUNK_ELEMS = 1 << 28
+
+
+def engine_matrix(X: torch.Tensor):
+    """Return ``(X32, element_order)``: the float32 row-major matrix the kernels read and whether
+    its dots must be summed element-wise.
+
+    The reference dispatches float32, float64 and float16 (``AT_DISPATCH_FLOATING_TYPES_AND_HALF``,
+    src/coresets/cuda/kernels/warp.cu:167) and for the last two converts every element to float
+    before an element-wise fma chain (``_shared.cuh:55-58``).  Converting the matrix once gives
+    the same float values (float16 -> float32 is exact, float64 -> float32 rounds to nearest as
+    the kernel's cast does), so those inputs run the float32 kernels with the element-wise order."""
+    if X.dtype == torch.float32:
+        return X.contiguous(), False
+    if X.dtype not in (torch.float16, torch.float64):
+        raise ValueError(f"X must be float32, float64 or float16 (the reference's dispatch), got {X.dtype}")
+    N, D = X.shape
+    out = torch.empty((N, D), dtype=torch.float32, device=X.device)
+    chunk = max(1, _CONVERT_CHUNK_ELEMS // max(D, 1))
+    for a in range(0, N, chunk):
+        out[a : a + chunk].copy_(X[a : a + chunk])
+    return out, True
+
+
 def default_mode() -> int:
     m = os.environ.get("CORESETS_B200_MODE", "prune").strip().lower()
     if m not in ("prune", "dense"):
@@ -76,11 +100,11 @@ class ShardEngine:
     def __init__(self, X_local: torch.Tensor, norms: torch.Tensor, cap: int, *, shard_offset: int = 0,
                  world_size: int = 1, group=None, mode: Optional[int] = None,
                  h: Optional[torch.Tensor] = None, voronoi: Optional[torch.Tensor] = None,
-                 record: bool = True):
+                 record: bool = True, element_order: bool = False):
         if X_local.dim() != 2:
             raise ValueError(f"X_local must be 2-D, got shape {tuple(X_local.shape)}")
         if X_local.dtype != torch.float32:
-            raise ValueError(f"the sm_100a engine computes in float32 only, got {X_local.dtype}")
+            raise ValueError(f"the engine reads float32 rows (see engine_matrix), got {X_local.dtype}")
         if not X_local.is_contiguous():
             raise ValueError("X_local must be contiguous (row-major)")
         self.native = _native.get_native()
@@ -94,6 +118,7 @@ class ShardEngine:
         self.world_size = int(world_size)
         self.group = group
         self.mode = default_mode() if mode is None else int(mode)
+        self.element_order = bool(element_order)
         dev = self.device
         f32, i32, i64 = torch.float32, torch.int32, torch.int64
         n_alloc = max(self.N_local, 1)
@@ -163,6 +188,7 @@ class ShardEngine:
         for r, ptr in enumerate(self.peer_ptrs):
             s.peer_win[r] = ptr
         s.xchg_timeout_ms = int(os.environ.get("CORESETS_B200_XCHG_TIMEOUT_MS", "10000"))
+        s.flags = _native.F_ELEMENT_ORDER if self.element_order else 0
         return s
 
     def rebind(self, *, h: Optional[torch.Tensor] = None, voronoi: Optional[torch.Tensor] = None) -> None:

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define CS_ABI_VERSION 3
+#define CS_ABI_VERSION 4
 
 #if defined(__GNUC__)
 #define CS_API __attribute__((visibility("default")))
@@ -54,6 +54,11 @@ extern "C" {
                               update, so results are identical to CS_MODE_PRUNE; X is streamed by
                               bulk asynchronous (TMA) copies when D % 4 == 0 and 32 <= D <= 1024 */
 #define CS_MODE_DENSE_LDG 3u /* dense mode with plain 128-bit loads (the path other row widths take) */
+/* cs_state.flags */
+#define CS_F_ELEMENT_ORDER 1u /* every dot product sums element-wise (lane l takes elements l, l+32,
+                              ... with one fma each) even when D % 4 == 0: the order the reference uses
+                              for float16 / float64 inputs (_shared.cuh:55-58), whose rows the caller
+                              passes converted to float32 */
 /* cs_commit_bound flags */
 #define CS_RULE_NONE 0u    /* plain FPS: no separation bookkeeping */
 #define CS_RULE_SIM_SINGLE 1u   /* commit_center_with_sep_kernel rules (commit.cu:41-51) */
@@ -114,7 +119,7 @@ typedef struct cs_state {
                               into THIS process (peer_win[rank] is the local one); each holds
                               cs_xchg_window_words() zero-initialised 32-bit words             */
     int32_t xchg_timeout_ms; /* bound of the flag wait (0 = 10 s); on expiry status becomes 3  */
-    int32_t reserved0;
+    int32_t flags;         /* CS_F_* bits                                                     */
 } cs_state;
 
 typedef void* cs_stream; /* cudaStream_t */

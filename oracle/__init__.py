@@ -6,6 +6,7 @@ C-contiguous; ``voronoi`` is int64 as in the reference (src/coresets/cuda/fps.py
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import subprocess
 from pathlib import Path
@@ -60,8 +61,21 @@ def lib():
         L.oracle_simulate_sharded.argtypes = [_f32p, _f32p, _int, _int, _i64p, _f32p, _i64p, _f32p, _f32p,
                                               _i64, ctypes.c_double, _i64, ctypes.POINTER(_i64),
                                               ctypes.POINTER(ctypes.c_float)]
+        L.oracle_set_element_order.restype = None
+        L.oracle_set_element_order.argtypes = [_int]
         _lib = L
     return _lib
+
+
+@contextlib.contextmanager
+def element_order(on: bool = True):
+    """Within the block every dot is summed element-wise (the reference's order for float16 /
+    float64 inputs, _shared.cuh:55-58); the caller passes the rows converted to float32."""
+    lib().oracle_set_element_order(1 if on else 0)
+    try:
+        yield
+    finally:
+        lib().oracle_set_element_order(0)
 
 
 def _c(a, dt):

@@ -48,9 +48,16 @@ static int better(float va, int64_t ia, float vb, int64_t ib) {
  * runs afterwards (warp.cu:35-37, commit.cu:92-94): lane l accumulates float4 chunks
  * l, l+32, ...; then p[j] += p[j+off] for off = 16,8,4,2,1.  Lane 0 holds the result.
  */
+static int g_element_order = 0;
+
+/* Inputs that were float16 / float64 take the element-wise branch of warp_dot for every D
+ * (_shared.cuh:55-58: `dot += (float) row[i] * (float) c[i]`, one fma per element); the caller
+ * hands this oracle the converted float rows and switches the branch here. */
+ORACLE_API void oracle_set_element_order(int on) { g_element_order = on; }
+
 static float ref_warp_dot(const float* row, const float* c, int D) {
     float p[32];
-    if (D % 4 == 0) {
+    if (D % 4 == 0 && !g_element_order) {
         const int d4 = D / 4;
         for (int l = 0; l < 32; ++l) {
             float acc = 0.0f;

@@ -32,3 +32,15 @@ def with_duplicates(X: np.ndarray, n_dup: int, seed: int) -> np.ndarray:
     dst = rng.integers(0, X.shape[0], size=n_dup)
     X[dst] = X[src]
     return X
+
+
+def as_dtype(X: np.ndarray, dtype: str) -> np.ndarray:
+    """The float32 matrix as a float16 / float64 input.  float64 values get low-order bits that
+    do not survive the conversion back to float32, so that rounding is exercised."""
+    if dtype == "float32":
+        return X
+    if dtype == "float16":
+        return X.astype(np.float16)
+    if dtype == "float64":
+        return X.astype(np.float64) * 1.000000123
+    raise ValueError(dtype)

@@ -159,7 +159,8 @@ class FakeNative:
             a["v"][l] = i
         a["X_sel"][i] = row
         if i > 0:
-            a["dSL"][:i] = oracle.dsl_quarter(a["X_sel"][: i + 1], a["norms_sel"][: i + 1], i)
+            with oracle.element_order(bool(s.flags & 1)):
+                a["dSL"][:i] = oracle.dsl_quarter(a["X_sel"][: i + 1], a["norms_sel"][: i + 1], i)
 
     def fps_step(self, s, mode, stream):
         a = self._arrays(s)
@@ -171,14 +172,15 @@ class FakeNative:
         N = s.N_local
         if N > 0:
             v64 = a["v"].astype(np.int64)
-            if i == 0:
-                oracle.fps_update(a["X"], a["norms"], a["X_sel"][0], a["norms_sel"][0], a["h"], v64, 0)
-                live = int((a["h"] >= 0).sum())
-            else:
-                live = oracle.voronoi_update(a["X"], a["norms"], a["X_sel"][i], a["norms_sel"][i],
-                                             a["dSL"][:i], a["h"], v64, i)
-                if mode & MODE_DENSE:
-                    live = int((~(a["h"] < 0)).sum())
+            with oracle.element_order(bool(s.flags & 1)):
+                if i == 0:
+                    oracle.fps_update(a["X"], a["norms"], a["X_sel"][0], a["norms_sel"][0], a["h"], v64, 0)
+                    live = int((a["h"] >= 0).sum())
+                else:
+                    live = oracle.voronoi_update(a["X"], a["norms"], a["X_sel"][i], a["norms_sel"][i],
+                                                 a["dSL"][:i], a["h"], v64, i)
+                    if mode & MODE_DENSE:
+                        live = int((~(a["h"] < 0)).sum())
             a["v"][:] = v64.astype(np.int32)
             ctl.live_rows = live
             val, li = oracle.argmax(a["h"])

@@ -42,13 +42,20 @@ CASES = [
     ("c1_20000x64", "gaussian_mixture", dict(N=20000, D=64, n_comp=16, seed=0), 512, None),
     ("dups_3000x16", "dups", dict(N=3000, D=16, seed=5), 1500, None),
     ("seeded_5000x64", "gaussian_mixture", dict(N=5000, D=64, n_comp=8, seed=3), 200, [17, 4000, 123]),
+    # float16 / float64 inputs (the reference's AT_DISPATCH_FLOATING_TYPES_AND_HALF, warp.cu:167)
+    ("f16_2500x128", "gaussian_mixture", dict(N=2500, D=128, n_comp=8, seed=11), 200, None, "float16"),
+    ("f16_800x50", "gaussian_mixture", dict(N=800, D=50, n_comp=8, seed=12), 64, None, "float16"),
+    ("f64_1500x64", "gaussian_mixture", dict(N=1500, D=64, n_comp=8, seed=13), 128, None, "float64"),
+    ("f64_1200x256", "gaussian_mixture", dict(N=1200, D=256, n_comp=8, seed=14), 100, [5, 900], "float64"),
 ]
 
 
-def make_x(gen: str, kw: dict) -> np.ndarray:
+def make_x(gen: str, kw: dict, dtype: str = "float32") -> np.ndarray:
     if gen == "dups":
-        return tdata.with_duplicates(tdata.clustered_jitter(kw["N"], kw["D"], seed=kw["seed"]), 600, seed=9)
-    return getattr(tdata, gen)(**kw)
+        X = tdata.with_duplicates(tdata.clustered_jitter(kw["N"], kw["D"], seed=kw["seed"]), 600, seed=9)
+    else:
+        X = getattr(tdata, gen)(**kw)
+    return tdata.as_dtype(X, dtype)
 
 
 def load_reference():
@@ -99,7 +106,8 @@ def compare_with_engine(name, X, K, seeds, sel_ref, eps_ref, h_ref, v_ref):
     """Side-by-side run of this repository's engine on the same device tensor (diagnostic)."""
     from coresets_b200 import engine
     norms = engine.row_norms(X)
-    eng = engine.ShardEngine(X.contiguous(), norms, K)
+    X32, element_order = engine.engine_matrix(X.contiguous())
+    eng = engine.ShardEngine(X32, norms, K, element_order=element_order)
     eng.init_state()
     for s_ in ([0] if seeds is None else seeds):
         eng.pick_forced(int(s_))
@@ -251,6 +259,7 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=str(ROOT / "golden_out"))
     ap.add_argument("--compare", action="store_true", help="also run this repository's engine side by side")
+    ap.add_argument("--cases", default="", help="only the FPS cases whose name contains this text (and no accretion)")
     a = ap.parse_args()
     out = Path(a.out)
     out.mkdir(parents=True, exist_ok=True)
@@ -261,14 +270,17 @@ def main() -> None:
     torch.cuda.set_device(0)
     dist.init_process_group("nccl", rank=0, world_size=1)
     dev = torch.device("cuda:0")
-    for name, gen, kw, K, seeds in CASES:
-        X_np = make_x(gen, kw)
+    for name, gen, kw, K, seeds, *rest in CASES:
+        if a.cases and a.cases not in name:
+            continue
+        dtype = rest[0] if rest else "float32"
+        X_np = make_x(gen, kw, dtype)
         X = torch.from_numpy(X_np).to(dev)
         seed_t = None if seeds is None else torch.tensor(seeds, dtype=torch.long)
         sel_api = coresets.fps_cuda(X, K, seed=seed_t).cpu().numpy().astype(np.int64)
         sel, eps, norms, h, v = transparent_run(coresets, ext, X, K, seeds)
         assert np.array_equal(sel, sel_api), f"{name}: transparent loop diverged from fps_cuda"
-        rec = dict(generator=gen, K=K, selected=sel_api, eps=eps, norms=norms, h=h, voronoi=v,
+        rec = dict(generator=gen, K=K, dtype=dtype, selected=sel_api, eps=eps, norms=norms, h=h, voronoi=v,
                    seeds=np.asarray(seeds if seeds is not None else [0], dtype=np.int64),
                    **{f"gen_{k}": v_ for k, v_ in kw.items()})
         if seeds is None or len(seeds) == 1:
@@ -280,6 +292,9 @@ def main() -> None:
         print(f"[golden] {name}: K={K} first={sel_api[:5].tolist()} last={sel_api[-3:].tolist()}", flush=True)
         if a.compare:
             compare_with_engine(name, X, K, seeds, sel_api, eps, h, v)
+    if a.cases:
+        dist.destroy_process_group()
+        return
     accrete_goldens(coresets, dev, out, a.compare)
     if a.compare:
         midsize_accrete_compare(coresets, dev, out)

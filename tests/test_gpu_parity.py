@@ -29,7 +29,8 @@ def run_engine(X_np, k, *, mode=MODE_PRUNE, seed=(0,), graph=True, monkeypatch=N
     norms = engine.row_norms(X)
     if monkeypatch is not None:
         monkeypatch.setenv("CORESETS_B200_GRAPH", "1" if graph else "0")
-    eng = engine.ShardEngine(X, norms, k, mode=mode)
+    X32, element_order = engine.engine_matrix(X)
+    eng = engine.ShardEngine(X32, norms, k, mode=mode, element_order=element_order)
     eng.init_state()
     for s in seed:
         eng.pick_forced(int(s))
@@ -40,7 +41,8 @@ def run_engine(X_np, k, *, mode=MODE_PRUNE, seed=(0,), graph=True, monkeypatch=N
 
 
 def assert_matches_oracle(eng, X_np, norms_np, k, seed=(0,)):
-    o_sel, o_eps, o_h, o_v = oracle.fps_cuda(X_np, norms_np, k, seed=np.asarray(seed, dtype=np.int64))
+    with oracle.element_order(X_np.dtype != np.float32):
+        o_sel, o_eps, o_h, o_v = oracle.fps_cuda(X_np.astype(np.float32), norms_np, k, seed=np.asarray(seed, dtype=np.int64))
     N = X_np.shape[0]
     np.testing.assert_array_equal(eng.selected.cpu().numpy(), o_sel)
     np.testing.assert_array_equal(bits(eng.eps.cpu().numpy()), bits(o_eps))
@@ -85,6 +87,33 @@ def test_dense_mode_is_bit_identical(N, D, k):
     X = gaussian_mixture(N, D, 8, seed=N + D)
     eng, norms = run_engine(X, k, mode=MODE_DENSE)
     assert_matches_oracle(eng, X, norms, k)
+
+
+@pytest.mark.parametrize("dtype", ["float16", "float64"])
+@pytest.mark.parametrize("N,D,k", [(3000, 128, 200), (1500, 50, 64), (2000, 64, 100), (900, 1024, 40)])
+@pytest.mark.parametrize("mode", [MODE_PRUNE, MODE_DENSE])
+def test_float16_and_float64_inputs(dtype, N, D, k, mode):
+    """Inputs the reference sums element-wise after a cast to float (_shared.cuh:55-58)."""
+    from tests.data import as_dtype
+    X = as_dtype(gaussian_mixture(N, D, 8, seed=N + D), dtype)
+    eng, norms = run_engine(X, k, mode=mode)
+    assert_matches_oracle(eng, X, norms, k)
+
+
+def test_fps_cuda_accepts_float16_and_float64():
+    from tests.data import as_dtype
+    import coresets_b200
+    Xf = gaussian_mixture(2000, 96, 8, seed=5)
+    for dtype in ("float16", "float64"):
+        X = as_dtype(Xf, dtype)
+        Xd = torch.from_numpy(X).cuda()
+        sel = coresets_b200.fps_cuda(Xd, 150)
+        norms = (Xd * Xd).sum(dim=1).to(torch.float32).cpu().numpy()
+        with oracle.element_order():
+            o_sel, _, _, _ = oracle.fps_cuda(X.astype(np.float32), norms, 150)
+        np.testing.assert_array_equal(sel.cpu().numpy(), o_sel)
+    with pytest.raises(ValueError):
+        coresets_b200.fps_cuda(torch.zeros(10, 4, dtype=torch.bfloat16, device="cuda"), 2)
 
 
 @pytest.mark.parametrize("N,D,k", [(4097, 128, 300), (2500, 256, 100), (900, 1024, 48), (20000, 36, 100)])
@@ -220,6 +249,22 @@ def test_multi_rank_kernels_on_one_device(sizes):
         np.testing.assert_array_equal(bits(e.h[:n].cpu().numpy()), bits(o_h[offs[r] : offs[r] + n]))
         np.testing.assert_array_equal(e.voronoi[:n].cpu().numpy().astype(np.int64), o_v[offs[r] : offs[r] + n])
         assert torch.equal(e.X_sel, engs[0].X_sel)
+
+
+@pytest.mark.parametrize("sizes,D", [([1000, 1003], 64), ([0, 700, 0, 650], 128), ([301, 299, 2, 300], 256)])
+def test_multi_rank_kernels_dense_mode(sizes, D):
+    """The dense kernel (bulk-copy ring) publishing candidates for world_size > 1."""
+    N, k = sum(sizes), 100
+    X = with_duplicates(gaussian_mixture(N, D, 8, seed=N + D), 20, seed=2)
+    engs, norms, offs = _emulate_ranks(X, sizes, k, first=3, mode=MODE_DENSE)
+    o_sel, o_eps, o_h, o_v = oracle.fps_sharded(X, norms, k, sizes, first=3)
+    for r, e in enumerate(engs):
+        assert e.check_status().n_sel == k
+        np.testing.assert_array_equal(e.selected.cpu().numpy(), o_sel)
+        np.testing.assert_array_equal(bits(e.eps.cpu().numpy()), bits(o_eps))
+        n = sizes[r]
+        np.testing.assert_array_equal(bits(e.h[:n].cpu().numpy()), bits(o_h[offs[r] : offs[r] + n]))
+        np.testing.assert_array_equal(e.voronoi[:n].cpu().numpy().astype(np.int64), o_v[offs[r] : offs[r] + n])
 
 
 def test_large_shard_properties():

@@ -58,7 +58,22 @@ def test_fps_cuda_validation(fake_native):
     with pytest.raises(ValueError):
         fps_mod.fps(X, 2, seed=torch.tensor([], dtype=torch.long))
     with pytest.raises(ValueError):
-        fps_mod.fps(X.double(), 2)
+        fps_mod.fps(X.to(torch.bfloat16), 2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float64])
+@pytest.mark.parametrize("N,D,k", [(400, 64, 40), (333, 10, 30)])
+def test_fps_cuda_float16_and_float64(fake_native, dtype, N, D, k):
+    """Norms in the input's own dtype (fps.py:34), rows cast to float, dots summed element-wise
+    (_shared.cuh:55-58)."""
+    X = torch.from_numpy(gaussian_mixture(N, D, 8, seed=N)).to(dtype)
+    if dtype == torch.float64:
+        X = X * 1.000000123
+    sel, eps = fps_mod.fps(X, k, return_epsilons=True)
+    with oracle.element_order():
+        o_sel, o_eps, _, _ = oracle.fps_cuda(X.float().numpy(), _norms_t(X), k)
+    np.testing.assert_array_equal(sel.numpy(), o_sel)
+    np.testing.assert_array_equal(eps.numpy().view(np.int32), o_eps.view(np.int32))
 
 
 def test_fps_cuda_requires_cuda_tensor():

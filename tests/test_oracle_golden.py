@@ -28,7 +28,12 @@ def load_case(name):
         X = tdata.with_duplicates(tdata.clustered_jitter(kw["N"], kw["D"], seed=kw["seed"]), 600, seed=9)
     else:
         X = getattr(tdata, gen)(**kw)
-    return z, X
+    return z, tdata.as_dtype(X, str(z["dtype"]) if "dtype" in z.files else "float32")
+
+
+def f32(X):
+    """The float rows the kernels see, and whether the dots are summed element-wise."""
+    return np.ascontiguousarray(X.astype(np.float32)), X.dtype != np.float32
 
 
 def bits(a):
@@ -43,21 +48,25 @@ def test_golden_files_present():
 def test_oracle_reproduces_reference_cuda(name):
     z, X = load_case(name)
     K = int(z["K"])
-    sel, eps, h, v = oracle.fps_cuda(X, z["norms"], K, seed=z["seeds"])
+    X, elem = f32(X)
+    with oracle.element_order(elem):
+        sel, eps, h, v = oracle.fps_cuda(X, z["norms"], K, seed=z["seeds"])
     np.testing.assert_array_equal(sel, z["selected"])
     np.testing.assert_array_equal(bits(eps), bits(z["eps"]))
     np.testing.assert_array_equal(bits(h), bits(z["h"]))
     np.testing.assert_array_equal(v, z["voronoi"].astype(np.int64))
 
 
-@pytest.mark.parametrize("name", [n for n in GPU_CASES if n != "seeded_5000x64"])
+@pytest.mark.parametrize("name", [n for n in GPU_CASES if n not in ("seeded_5000x64", "f64_1200x256")])
 @pytest.mark.parametrize("world", [1, 4])
 def test_oracle_sharded_reproduces_reference_fps_sharded(name, world):
     z, X = load_case(name)
     K, N = int(z["K"]), X.shape[0]
     base = N // world
     sizes = [base] * (world - 1) + [N - base * (world - 1)]
-    sel, eps, _, _ = oracle.fps_sharded(X, z["norms"], K, sizes)
+    X, elem = f32(X)
+    with oracle.element_order(elem):
+        sel, eps, _, _ = oracle.fps_sharded(X, z["norms"], K, sizes)
     np.testing.assert_array_equal(sel, z["sharded_selected"])
     assert np.isinf(z["sharded_eps"][0]) and np.isinf(eps[0])
     np.testing.assert_array_equal(bits(eps), bits(z["sharded_eps"]))

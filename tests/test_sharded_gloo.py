@@ -71,6 +71,25 @@ def test_fps_sharded_matches_oracle(tmp_path, sizes, k, seed):
         np.testing.assert_array_equal(eps.view(np.int32), o_eps.view(np.int32))
 
 
+@pytest.mark.parametrize("dtype", ["float16", "float64"])
+def test_fps_sharded_float16_and_float64(tmp_path, dtype):
+    """Non-float32 shards: norms in the input's dtype, rows cast to float, element-wise dots."""
+    import torch
+    from tests.data import as_dtype
+    sizes, k = [150, 153], 48
+    X = as_dtype(with_duplicates(clustered_jitter(sum(sizes), 16, seed=9), 10, seed=4), dtype)
+    np.save(tmp_path / "x.npy", X)
+    cfg = dict(x_path=str(tmp_path / "x.npy"), sizes=sizes, k=k, seed=None, out_dir=str(tmp_path))
+    _run(2, cfg)
+    t = torch.from_numpy(X)
+    norms = (t * t).sum(dim=1).to(torch.float32).numpy()
+    with oracle.element_order():
+        o_sel, o_eps, _, _ = oracle.fps_sharded(X.astype(np.float32), norms, k, sizes)
+    for r in range(2):
+        np.testing.assert_array_equal(np.load(tmp_path / f"sel_{r}.npy"), o_sel)
+        np.testing.assert_array_equal(np.load(tmp_path / f"eps_{r}.npy").view(np.int32), o_eps.view(np.int32))
+
+
 def test_checkpoint_cadence_and_resume(tmp_path):
     sizes, k = [200, 203], 40
     X = clustered_jitter(sum(sizes), 8, seed=11)
