@@ -41,13 +41,17 @@ def accrete(
         )
     if _REQUIRE_CUDA and not X_anchor.is_cuda:
         raise ValueError(f"X_anchor must be on a CUDA device, got {X_anchor.device}")
-    if X_anchor.dtype != torch.float32:
-        raise ValueError(f"accrete computes in float32; got {X_anchor.dtype}")
+    if X_anchor.dtype not in (torch.float32, torch.float16):
+        # float64 is not offered: the reference's reconstruct step cannot finish with it either (it
+        # assigns a float64 result into the float32 h, which torch's index_put rejects)
+        raise ValueError(f"X_anchor must be float32 or float16, got {X_anchor.dtype}")
     n_total, dim = n_anchor + n_cand, int(X_anchor.shape[1])
     X = (torch.cat([X_anchor, X_candidates], dim=0) if n_cand > 0 else X_anchor).contiguous()
     norms = _engine.row_norms(X)
     max_k, max_sel = resolve_max_k(max_k, n_total, dim, X.element_size(), X.device, strict=True, collective=False)
     layout = ShardLayout(rank=0, world_size=1, sizes=[n_total], offsets=[0])
-    driver = AccreteDriver(X, norms, layout, anchor_order.tolist(), n_anchor, n_total, max_k, max_sel,
-                           flavour="single", verbose=verbose, profile=profile, trace_path=trace_path)
+    X32, element_order = _engine.engine_matrix(X)
+    driver = AccreteDriver(X32, norms, layout, anchor_order.tolist(), n_anchor, n_total, max_k, max_sel,
+                           flavour="single", verbose=verbose, profile=profile, trace_path=trace_path,
+                           X_src=X if element_order else None)
     return driver.run()

@@ -53,7 +53,11 @@ class AccreteDriver:
     def __init__(self, X_local: Tensor, norms_local: Tensor, layout: ShardLayout, anchor_order: List[int],
                  n_anchor: int, n_global: int, max_k: int, max_sel: int, *, flavour: str, verbose: bool,
                  profile: bool, trace_path: Optional[str], checkpoint_path: Optional[str] = None,
-                 resume_from: Optional[str] = None, checkpoint_every: int = 0):
+                 resume_from: Optional[str] = None, checkpoint_every: int = 0,
+                 X_src: Optional[Tensor] = None):
+        """``X_local`` is the float32 matrix the kernels read.  ``X_src`` is the caller's matrix when
+        it was float16 / float64: the kernels then sum element-wise (``engine.engine_matrix``) and the
+        reconstruct step multiplies in the caller's dtype, as the reference does."""
         assert flavour in ("single", "sharded")
         self.flavour = flavour
         self.multi = flavour == "sharded"
@@ -71,7 +75,8 @@ class AccreteDriver:
         self.rules = RULE_SIM_SHARDED if self.multi else RULE_SIM_SINGLE
 
         world = layout.world_size if self.multi else 1
-        kw = dict(shard_offset=layout.shard_offset, world_size=world)
+        self.X_src = X_src
+        kw = dict(shard_offset=layout.shard_offset, world_size=world, element_order=X_src is not None)
         self.E = _engine.ShardEngine(X_local, norms_local, self.max_sel, **kw)
         self.S = _engine.ShardEngine(X_local, norms_local, self.max_sel, record=False, **kw)
         self.E.init_state()
@@ -193,6 +198,13 @@ class AccreteDriver:
                     X_added = self.E.X_sel[n_snap : n_snap + m]
                     n_added = self.E.norms_sel[n_snap : n_snap + m]
                     X_aff = self.E.X[affected]
+                    if self.X_src is not None:
+                        # float16 / float64 input: the product runs in the caller's dtype.  The
+                        # single-GPU reference gathers the added rows from X (reconstruct.py:102),
+                        # the sharded one keeps them in an X_sel of X's dtype that was filled from
+                        # the float32 exchange pack (sharded.py:52, multi.cu:245)
+                        X_aff = self.X_src[affected]
+                        X_added = X_added.to(self.X_src.dtype) if self.multi else self.X_src[added_t[:m]]
                     n_aff = self.E.norms[affected]
                     cnt = affected.numel()
                     best = torch.full((cnt,), float("inf"), dtype=torch.float32, device=self.device)
@@ -254,7 +266,8 @@ class AccreteDriver:
         world = self.layout.world_size if self.multi else 1
         while len(self._lanes) < n:
             self._lanes.append(_engine.ShardEngine(self.E.X, self.E.norms, self.max_sel, record=False,
-                                                   shard_offset=self.layout.shard_offset, world_size=world))
+                                                   shard_offset=self.layout.shard_offset, world_size=world,
+                                                   element_order=self.E.element_order))
         return self._lanes[:n]
 
     def _simulate_lanes(self, engines, probes) -> List[bool]:

@@ -64,8 +64,10 @@ def accrete_voronoi_multi_sharded(
         raise ValueError(f"N_A_global={N_A_global} must be in [0, N_global={N_global}]")
     if _REQUIRE_CUDA and not X_local.is_cuda:
         raise ValueError(f"X_local must be on a CUDA device, got {X_local.device}")
-    if X_local.dtype != torch.float32:
-        raise ValueError(f"accrete_sharded computes in float32; got {X_local.dtype}")
+    if X_local.dtype not in (torch.float32, torch.float16):
+        # float64 is not offered: the reference's reconstruct step cannot finish with it either (it
+        # assigns a float64 result into the float32 h, which torch's index_put rejects)
+        raise ValueError(f"X_local must be float32 or float16, got {X_local.dtype}")
 
     X_local = X_local.contiguous()
     sizes = [int(s) for s in shard_sizes]
@@ -98,10 +100,11 @@ def accrete_voronoi_multi_sharded(
             raise ValueError(f"n_target={n_target} exceeds the pool size N_global={N_global}")
         max_sel = n_target
 
-    driver = AccreteDriver(X_local, norms_local, layout, idx_A.tolist(), N_A_global, N_global, max_k, max_sel,
+    X32, element_order = _engine.engine_matrix(X_local)
+    driver = AccreteDriver(X32, norms_local, layout, idx_A.tolist(), N_A_global, N_global, max_k, max_sel,
                            flavour="sharded", verbose=verbose, profile=profile, trace_path=trace_path,
                            checkpoint_path=checkpoint_path, resume_from=resume_from,
-                           checkpoint_every=checkpoint_every)
+                           checkpoint_every=checkpoint_every, X_src=X_local if element_order else None)
     return driver.run()
 
 

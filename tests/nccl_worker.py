@@ -64,12 +64,12 @@ def accrete_mode(cfg, rank, world, dev):
     import coresets_b200
     from coresets_b200.cuda.multi.layout import compute_shard_layout
     from tests.data import clustered_jitter, gaussian_mixture
-    from tests.golden.make_golden_gpu import ACCRETE_CASES
+    from tests.golden.make_golden_gpu import ACCRETE_CASES, accrete_case_matrix
     golden = ROOT / "tests" / "golden"
     failures = []
     for name, c in ACCRETE_CASES.items():
         z = np.load(golden / f"{name}.npz")
-        X_np = clustered_jitter(c["N"], c["D"], seed=42) if c["gen"] == "jitter" else gaussian_mixture(c["N"], c["D"], 12, seed=c["N"])
+        X_np = accrete_case_matrix(c)
         sizes, offs = compute_shard_layout(c["N"], world)
         Xl = torch.from_numpy(np.ascontiguousarray(X_np[offs[rank] : offs[rank] + sizes[rank]])).to(dev)
         order = torch.from_numpy(z["anchor_order"]).to(dev)

@@ -17,18 +17,18 @@ def _cases():
 
 
 def test_accrete_golden_files_present():
-    assert len(_cases()) >= 3
+    assert len(_cases()) >= 4
 
 
-@pytest.mark.parametrize("name", ["acc_8192x32_k2048", "acc_16383x128_k1024", "acc_mix_20000x64_k512_fps"])
+@pytest.mark.parametrize("name", ["acc_8192x32_k2048", "acc_16383x128_k1024", "acc_mix_20000x64_k512_fps",
+                                  "acc_f16_4000x32_k256"])
 def test_accrete_matches_reference(name, tmp_path):
     import coresets_b200
-    from tests.data import clustered_jitter, gaussian_mixture
     from tests.golden.make_golden_accrete_cpu import read_trace
+    from tests.golden.make_golden_gpu import accrete_case_matrix
     c = _cases()[name]
     z = np.load(GOLDEN / f"{name}.npz")
-    X_np = clustered_jitter(c["N"], c["D"], seed=42) if c["gen"] == "jitter" else gaussian_mixture(c["N"], c["D"], 12, seed=c["N"])
-    X = torch.from_numpy(X_np).cuda()
+    X = torch.from_numpy(accrete_case_matrix(c)).cuda()
     na = c["n_anchor"]
     order = torch.from_numpy(z["anchor_order"]).cuda()
     if c["order"] == "fps":   # the anchor ordering itself is the reference's fps_cuda output
