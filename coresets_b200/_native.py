@@ -20,6 +20,7 @@ CS_CTL_BYTES = 256
 MODE_PRUNE = 0
 MODE_DENSE = 1
 MODE_DENSE_LDG = 3
+MODE_PRUNE_INLINE = 2
 RULE_NONE = 0
 RULE_SIM_SINGLE = 1
 RULE_SIM_SHARDED = 2

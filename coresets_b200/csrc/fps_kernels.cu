@@ -585,6 +585,229 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
     }
 }
 
+// ---- prune mode with deferred rows -------------------------------------------------------------------
+// In prune mode few rows pass the triangle test and they are scattered, so walking them where
+// they are met leaves a warp with one or two row loads in flight and a long dependent chain per
+// super-tile.  Here the scan and the distance work are decoupled: a warp streams h / voronoi of
+// its super-tiles (the next one is already in flight), applies the test, and pushes the rows that
+// need a distance onto a warp-private queue in shared memory; whenever the queue holds a full
+// batch, the batch is evaluated branch-free with all of its row loads in flight.  The arithmetic
+// per row, the update rule and the arg-max order are those of fps_step_kernel, so the bits match.
+constexpr int kQueueCap = 160;           // a batch remainder (< 16) plus one super-tile (128), padded
+
+template <int CPL, bool FULL, bool HALF>
+__global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_queue_kernel(const cs_state s, const int n_bound_smem) {
+    static_assert(kRowsPerLane == 4, "the deferred-row kernel reads four rows per lane");
+    extern __shared__ __align__(16) float s_dyn[];               // the first n_bound_smem triangle bounds
+    float* s_dsl = s_dyn;
+    __shared__ int2 s_queue[kWarps][kQueueCap];                  // (local row, bits of its h)
+    __shared__ u64 s_keys[kWarps];
+    __shared__ unsigned s_live[kWarps];
+    __shared__ int s_last;
+
+    Ctl* ctl = reinterpret_cast<Ctl*>(s.ctl);
+    const int i = ctl->n_sel;
+    if (i >= s.cap) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) ctl->status = ST_CAPACITY;
+        return;
+    }
+    const int D = s.D, d4 = D >> 2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = HALF ? (lane & 15) : lane;
+    const bool hi = HALF && lane >= 16;
+    const bool first = (i == 0);
+    const float nn = s.norms_sel[i];
+    float4 cen[CPL];
+    {
+        const float4* c4 = reinterpret_cast<const float4*>(s.X_sel + (int64_t)i * D);
+#pragma unroll
+        for (int c = 0; c < CPL; ++c)
+            cen[c] = (FULL || sub + 32 * c < d4) ? c4[sub + 32 * c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const int nb = i < n_bound_smem ? i : n_bound_smem;
+    for (int c = threadIdx.x; c < nb; c += blockDim.x) s_dsl[c] = s.dSL_quarter[c];
+    __syncthreads();
+
+    const int64_t N = s.N_local;
+    const int n32 = (int)N;
+    const int tiles = (int)((N + 127) >> 7);
+    const int whole_tiles = (int)(N >> 7);
+    const int nw = (int)gridDim.x * kWarps;
+    const float4* X4 = reinterpret_cast<const float4*>(s.X);
+    const bool vec_ok = ((((uintptr_t)s.h) | ((uintptr_t)s.voronoi)) & 15u) == 0;
+    const float kNegInf = __uint_as_float(0xff800000u);
+    float best_h = kNegInf;
+    int best_row = -1;
+    unsigned live_cnt = 0;
+    int2* q = s_queue[warp];
+    int qn = 0;                                                  // entries waiting (warp-uniform)
+    constexpr int BS = HALF ? 16 : (CPL >= 8 ? 1 : 8 / CPL);     // rows of a batch
+
+    // ---- one batch: entries q[base .. base+cnt), cnt <= BS; lane b < cnt finishes entry b --------
+    auto run_batch = [&](const int base, const int cnt) {
+        float mydot = 0.0f;
+        if (HALF) {
+            float4 a[8];
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                int e = 2 * b + (hi ? 1 : 0);
+                e = e < cnt ? e : cnt - 1;                       // an empty slot repeats the last entry
+                const int r = q[base + e].x;
+                a[b] = ld_stream4(X4 + (int64_t)r * d4 + (sub < d4 ? sub : 0));
+            }
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                float p = 0.0f;
+                if (sub < d4) p = __fadd_rn(p, chunk_dot(a[b], cen[0]));
+                p = __fadd_rn(p, 0.0f);                          // level 16 of the tree: the partner holds 0
+#pragma unroll
+                for (int off = 8; off > 0; off >>= 1) p = __fadd_rn(p, __shfl_xor_sync(kFull, p, off));
+                const float pa = __shfl_sync(kFull, p, 0), pb = __shfl_sync(kFull, p, 16);
+                if (lane == 2 * b) mydot = pa;
+                if (lane == 2 * b + 1) mydot = pb;
+            }
+        } else {
+            float4 a[BS][CPL];
+#pragma unroll
+            for (int b = 0; b < BS; ++b) {
+                const int r = q[base + (b < cnt ? b : cnt - 1)].x;
+                const float4* rp = X4 + (int64_t)r * d4;
+#pragma unroll
+                for (int c = 0; c < CPL; ++c)
+                    a[b][c] = ld_stream4(rp + ((FULL || lane + 32 * c < d4) ? lane + 32 * c : 0));
+            }
+#pragma unroll
+            for (int b = 0; b < BS; ++b) {
+                float p = 0.0f;
+#pragma unroll
+                for (int c = 0; c < CPL; ++c)
+                    if (FULL || lane + 32 * c < d4) p = __fadd_rn(p, chunk_dot(a[b][c], cen[c]));
+                p = warp_tree_sum(p);
+                if (lane == b) mydot = p;
+            }
+        }
+        if (lane < cnt) {
+            const int2 e = q[base + lane];
+            const int row = e.x;
+            float hq = __int_as_float(e.y);
+            const float d = sq_dist(__ldg(s.norms + row), nn, mydot);
+            if (d < hq) {
+                hq = d;
+                s.h[row] = d;
+                s.voronoi[row] = i;
+            }
+            // deferred rows come out of order: the full tie rule
+            if (hq > best_h || (hq == best_h && row < best_row)) { best_h = hq; best_row = row; }
+        }
+        __syncwarp();
+    };
+
+    auto load_tile = [&](const int t, float (&hq)[4], int (&vq)[4]) {
+        if (t >= tiles) return;
+        const int r0 = (t << 7) + 4 * lane;
+        if (vec_ok && t < whole_tiles) {
+            const float4 a = *reinterpret_cast<const float4*>(s.h + r0);
+            hq[0] = a.x; hq[1] = a.y; hq[2] = a.z; hq[3] = a.w;
+            if (!first) {
+                const int4 b = *reinterpret_cast<const int4*>(s.voronoi + r0);
+                vq[0] = b.x; vq[1] = b.y; vq[2] = b.z; vq[3] = b.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const bool in = r0 + j < n32;
+                hq[j] = in ? s.h[r0 + j] : kNegInf;              // rows past the end: not live, never the maximum
+                vq[j] = (in && !first) ? s.voronoi[r0 + j] : 0;
+            }
+        }
+    };
+
+    auto scan_tile = [&](const int t, float (&hq)[4], int (&vq)[4]) {
+        if (t >= tiles) return;
+        const int r0 = (t << 7) + 4 * lane;
+        unsigned need = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const bool live = !(hq[j] < 0.0f);                                 // warp.cu:28-30, 75-77
+            bool up = live;
+            if (!first && live) {
+                const float b = (vq[j] < nb) ? s_dsl[vq[j]] : __ldg(s.dSL_quarter + vq[j]);
+                up = !(b >= hq[j]);                                            // warp.cu:80-82
+            }
+            need |= up ? (1u << j) : 0u;
+        }
+        // rows that keep their h compete for the arg-max now (rows of a lane come in increasing
+        // order here, so '>' keeps the smallest row among equal values)
+        float tmax = kNegInf;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) tmax = fmaxf(tmax, (need >> j) & 1u ? kNegInf : hq[j]);
+        if (tmax > best_h) {
+            best_h = tmax;
+#pragma unroll
+            for (int j = 3; j >= 0; --j) best_row = (!((need >> j) & 1u) && hq[j] == tmax) ? r0 + j : best_row;
+        }
+        if (!__any_sync(kFull, need != 0u)) return;
+        // append this lane's rows behind those of the lower lanes
+        const int c = __popc(need);
+        int pre = c;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int o = __shfl_up_sync(kFull, pre, off);
+            if (lane >= off) pre += o;
+        }
+        const int total = __shfl_sync(kFull, pre, 31);
+        int w = qn + pre - c;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if ((need >> j) & 1u) q[w++] = make_int2(r0 + j, __float_as_int(hq[j]));
+        qn += total;
+        live_cnt += (unsigned)total;
+        __syncwarp();
+        while (qn >= BS) {
+            qn -= BS;
+            run_batch(qn, BS);
+        }
+    };
+
+    // two register sets: the loads of the next super-tile are in flight while this one is scanned
+    float ha[4], hb[4];
+    int va[4] = {0, 0, 0, 0}, vb[4] = {0, 0, 0, 0};
+    int t = (int)blockIdx.x * kWarps + warp;
+    load_tile(t, ha, va);
+    for (; t < tiles; t += 2 * nw) {
+        load_tile(t + nw, hb, vb);
+        scan_tile(t, ha, va);
+        load_tile(t + 2 * nw, ha, va);
+        scan_tile(t + nw, hb, vb);
+    }
+    if (qn > 0) run_batch(0, qn);
+
+    u64 best = best_row >= 0 ? make_key(best_h, s.shard_offset + best_row) : 0;
+    best = warp_max_key(best);
+    if (lane == 0) { s_keys[warp] = best; s_live[warp] = live_cnt; }
+    __syncthreads();
+    const int slot = (i + 1) & 1;
+    if (threadIdx.x == 0) {
+        u64 bk = 0;
+        unsigned lv = 0;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) { bk = s_keys[w] > bk ? s_keys[w] : bk; lv += s_live[w]; }
+        if (bk) atomicMax(&ctl->key[slot], bk);
+        if (lv) atomicAdd(&ctl->live_rows, (u64)lv);
+        __threadfence();
+        s_last = (atomicAdd(&ctl->ticket, 1u) == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const u64 k = *reinterpret_cast<volatile u64*>(&ctl->key[slot]);
+    if (s.world_size > 1) publish_candidate(s, ctl, k, key_idx(k) - s.shard_offset);
+    if (threadIdx.x == 0) {
+        ctl->ticket = 0;
+        ctl->n_sel = i + 1;
+    }
+}
+
 // ---- dense mode through the TMA engine -------------------------------------------------------------
 // Every live row is read in dense mode, so X can be streamed by bulk asynchronous copies
 // (cp.async.bulk, the 1-D TMA path: rows are contiguous, no tensor map needed) into a ring of
@@ -1224,6 +1447,39 @@ int launch_step(const cs_state* s, unsigned mode, cudaStream_t st, int sms) {
     return check_launch();
 }
 
+// prune mode with deferred rows (rows in whole 16-byte chunks, D <= 1024)
+template <int CPL, bool FULL, bool HALF = false>
+int launch_step_queue(const cs_state* s, cudaStream_t st, int sms) {
+    static thread_local size_t attr_set = 0, occ_smem = ~(size_t)0;
+    static thread_local int occ_blocks = 0;
+    const int n_bound = (int)(s->cap < kBoundSmemMax ? s->cap : kBoundSmemMax);
+    const size_t smem = (size_t)n_bound * sizeof(float);
+    if (smem > 32 * 1024 && smem > attr_set) {
+        if (cudaFuncSetAttribute(fps_step_queue_kernel<CPL, FULL, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess) {
+            g_last_cuda = cudaGetLastError();
+            return CS_E_LAUNCH;
+        }
+        attr_set = smem;
+    }
+    if (occ_smem != smem) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fps_step_queue_kernel<CPL, FULL, HALF>, kThreads,
+                                                          smem) != cudaSuccess || per_sm < 1) {
+            g_last_cuda = cudaGetLastError();
+            return CS_E_LAUNCH;
+        }
+        occ_blocks = per_sm;
+        occ_smem = smem;
+    }
+    const int64_t tiles = (s->N_local + 127) >> 7;
+    int64_t want = (tiles + kWarps - 1) / kWarps;
+    int64_t cap = (int64_t)sms * occ_blocks;     // persistent grid: a multiple of the SM count
+    int grid = (int)(want < 1 ? 1 : (want < cap ? want : cap));
+    fps_step_queue_kernel<CPL, FULL, HALF><<<grid, kThreads, smem, st>>>(*s, n_bound);
+    return check_launch();
+}
+
 template <int L, int CPL>
 int launch_lanes_t(const LaneSet& ls, unsigned mode, cudaStream_t st, int sms) {
     const size_t smem = (size_t)L * ls.s[0].D * sizeof(float);
@@ -1346,7 +1602,8 @@ int cs_commit_bound(const cs_state* s, uint32_t rules, cs_stream stream) {
 int cs_fps_step(const cs_state* s, uint32_t mode, cs_stream stream) {
     int rc = validate(s);
     if (rc) return rc;
-    if (mode != CS_MODE_PRUNE && mode != CS_MODE_DENSE && mode != CS_MODE_DENSE_LDG) return CS_E_ARG;
+    if (mode != CS_MODE_PRUNE && mode != CS_MODE_DENSE && mode != CS_MODE_DENSE_LDG && mode != CS_MODE_PRUNE_INLINE)
+        return CS_E_ARG;
     DevInfo d = device_info();
     if (!d.ok) return CS_E_DEVICE;
     cudaStream_t st = (cudaStream_t)stream;
@@ -1363,6 +1620,20 @@ int cs_fps_step(const cs_state* s, uint32_t mode, cs_stream stream) {
         return launch_step_tma<8, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d.sms);
     }
     if (element_order || (D & 3) != 0 || D > 1024) return launch_step<0, false>(s, mode, st, d.sms);
+    if (mode == CS_MODE_PRUNE && s->N_local > 0) {
+        switch (D) {
+            case 128: return launch_step_queue<1, true>(s, st, d.sms);
+            case 256: return launch_step_queue<2, true>(s, st, d.sms);
+            case 512: return launch_step_queue<4, true>(s, st, d.sms);
+            case 1024: return launch_step_queue<8, true>(s, st, d.sms);
+            default: break;
+        }
+        if (D <= 64) return launch_step_queue<1, false, true>(s, st, d.sms);
+        if (D < 128) return launch_step_queue<1, false>(s, st, d.sms);
+        if (D < 256) return launch_step_queue<2, false>(s, st, d.sms);
+        if (D < 512) return launch_step_queue<4, false>(s, st, d.sms);
+        return launch_step_queue<8, false>(s, st, d.sms);
+    }
     switch (D) {
         case 128: return launch_step<1, true>(s, mode, st, d.sms);
         case 256: return launch_step<2, true>(s, mode, st, d.sms);

@@ -49,7 +49,10 @@ extern "C" {
 #define CS_E_SCRATCH (-6)  /* D exceeds CS_NOALLOC_MAX_D, the fixed scratch of cs_fps_step_noalloc */
 
 /* cs_fps_step flags */
-#define CS_MODE_PRUNE 0u   /* rows excluded by the triangle bound are not loaded (default) */
+#define CS_MODE_PRUNE 0u   /* rows excluded by the triangle bound are not loaded (default); the rows
+                              that remain are queued and evaluated in batches */
+#define CS_MODE_PRUNE_INLINE 2u /* prune mode evaluating each remaining row where the scan meets it
+                              (the path rows of other widths take) */
 #define CS_MODE_DENSE 1u   /* every live row's distance is computed; the bound only masks the
                               update, so results are identical to CS_MODE_PRUNE; X is streamed by
                               bulk asynchronous (TMA) copies when D % 4 == 0 and 32 <= D <= 1024 */

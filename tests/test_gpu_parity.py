@@ -76,6 +76,24 @@ def test_fps_matches_oracle_prune(N, D, k):
     assert_matches_oracle(eng, X, norms, k)
 
 
+@pytest.mark.parametrize("N,D,k", [(33, 64, 20), (1000, 32, 128), (4097, 128, 300), (3000, 192, 64), (2500, 256, 200),
+                                   (900, 1024, 48), (1200, 100, 64), (20000, 36, 100), (130, 128, 130)])
+def test_fps_matches_oracle_prune_inline(N, D, k):
+    """Prune mode with the rows evaluated where the scan meets them (no queue)."""
+    from coresets_b200._native import MODE_PRUNE_INLINE
+    X = gaussian_mixture(N, D, 8, seed=N + D)
+    eng, norms = run_engine(X, k, mode=MODE_PRUNE_INLINE)
+    assert_matches_oracle(eng, X, norms, k)
+
+
+@pytest.mark.parametrize("N,D,k", [(130, 128, 130), (257, 64, 257), (5000, 16, 700), (40000, 8, 300), (12345, 48, 400)])
+def test_fps_matches_oracle_prune_more_shapes(N, D, k):
+    """Queue edge cases: every row selected, partial last super-tile, many rows per batch."""
+    X = with_duplicates(gaussian_mixture(N, D, 8, seed=N + D), min(50, N // 4), seed=1)
+    eng, norms = run_engine(X, k)
+    assert_matches_oracle(eng, X, norms, k)
+
+
 DENSE_SHAPES = [(33, 64, 20), (4097, 128, 300), (2500, 256, 100), (800, 50, 64), (900, 1024, 48), (3000, 192, 64),
                 (1200, 100, 64), (1000, 32, 128), (16383, 128, 256), (700, 1028, 40), (5, 128, 5), (20000, 36, 100),
                 (1500, 512, 64), (31, 8, 31), (1002, 64, 40), (258, 48, 30)]
