@@ -625,6 +625,9 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_queue_kernel
             cen[c] = (FULL || sub + 32 * c < d4) ? c4[sub + 32 * c] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     const int nb = i < n_bound_smem ? i : n_bound_smem;
+    // voronoi <= i (the row committed for this pick carries i itself), so with i inside the staged
+    // table every look-up stays within the block's shared memory
+    const bool all_bounds_staged = i < n_bound_smem;
     for (int c = threadIdx.x; c < nb; c += blockDim.x) s_dsl[c] = s.dSL_quarter[c];
     __syncthreads();
 
@@ -726,25 +729,41 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_queue_kernel
         if (t >= tiles) return;
         const int r0 = (t << 7) + 4 * lane;
         unsigned need = 0;
+        if (first) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const bool live = !(hq[j] < 0.0f);                                 // warp.cu:28-30, 75-77
-            bool up = live;
-            if (!first && live) {
-                const float b = (vq[j] < nb) ? s_dsl[vq[j]] : __ldg(s.dSL_quarter + vq[j]);
-                up = !(b >= hq[j]);                                            // warp.cu:80-82
+            for (int j = 0; j < 4; ++j) need |= !(hq[j] < 0.0f) ? (1u << j) : 0u;   // warp.cu:28-30
+        } else if (all_bounds_staged) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                // a selected row (h = -1) reads some bound too; the live test keeps it out
+                const float b = s_dsl[vq[j]];
+                need |= (!(hq[j] < 0.0f) && !(b >= hq[j])) ? (1u << j) : 0u;         // warp.cu:75-82
             }
-            need |= up ? (1u << j) : 0u;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float b = (vq[j] < nb) ? s_dsl[vq[j]] : __ldg(s.dSL_quarter + vq[j]);
+                need |= (!(hq[j] < 0.0f) && !(b >= hq[j])) ? (1u << j) : 0u;
+            }
         }
         // rows that keep their h compete for the arg-max now (rows of a lane come in increasing
         // order here, so '>' keeps the smallest row among equal values)
-        float tmax = kNegInf;
+        if (need == 0u) {
+            const float tmax = fmaxf(fmaxf(hq[0], hq[1]), fmaxf(hq[2], hq[3]));
+            if (tmax > best_h) {
+                best_h = tmax;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) tmax = fmaxf(tmax, (need >> j) & 1u ? kNegInf : hq[j]);
-        if (tmax > best_h) {
-            best_h = tmax;
+                for (int j = 3; j >= 0; --j) best_row = (hq[j] == tmax) ? r0 + j : best_row;
+            }
+        } else {
+            float tmax = kNegInf;
 #pragma unroll
-            for (int j = 3; j >= 0; --j) best_row = (!((need >> j) & 1u) && hq[j] == tmax) ? r0 + j : best_row;
+            for (int j = 0; j < 4; ++j) tmax = fmaxf(tmax, (need >> j) & 1u ? kNegInf : hq[j]);
+            if (tmax > best_h) {
+                best_h = tmax;
+#pragma unroll
+                for (int j = 3; j >= 0; --j) best_row = (!((need >> j) & 1u) && hq[j] == tmax) ? r0 + j : best_row;
+            }
         }
         if (!__any_sync(kFull, need != 0u)) return;
         // append this lane's rows behind those of the lower lanes
