@@ -308,8 +308,9 @@ class ShardEngine:
         """One fused step for several engines that share ``X`` (bisect probes): ``X`` is streamed
         once, every engine ends exactly as after its own ``step()``."""
         e0 = engines[0]
+        m = e0.mode if mode is None else int(mode)
         arr = (CsState * len(engines))(*[e.state for e in engines])
-        e0.native.fps_step_lanes(arr, len(engines), e0.mode if mode is None else int(mode), e0._stream())
+        e0.native.fps_step_lanes(arr, len(engines), m, e0._stream())
         for e in engines:
             e._unconsumed = True
 
