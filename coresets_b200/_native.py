@@ -13,7 +13,8 @@ from typing import Optional
 
 from . import build as _build
 
-CS_ABI_VERSION = 4
+CS_ABI_VERSION = 5
+SELECT_SCRATCH_BYTES = 8192
 F_ELEMENT_ORDER = 1
 CS_CTL_BYTES = 256
 
@@ -32,6 +33,7 @@ EXPORTS = (
     "cs_version", "cs_error_string", "cs_last_cuda_error", "cs_device_check", "cs_init_state",
     "cs_reset_ctl", "cs_force_pick", "cs_commit_bound", "cs_fps_step", "cs_sim_begin",
     "cs_sim_final_check", "cs_xchg_window_words", "cs_xchg_wait", "cs_scan_argmax", "cs_fps_step_lanes", "cs_fps_step_noalloc",
+    "cs_select_kth_largest",
 )
 
 
@@ -61,6 +63,11 @@ class CsState(ctypes.Structure):
         ("xchg_timeout_ms", ctypes.c_int32),
         ("flags", ctypes.c_int32),
     ]
+
+
+class SelectResult(ctypes.Structure):
+    """``cs_select_result`` of include/coresets_b200.h."""
+    _fields_ = [("value", ctypes.c_float), ("valid", ctypes.c_int32), ("n_alive", ctypes.c_int64)]
 
 
 class CtlView(ctypes.Structure):
@@ -120,6 +127,7 @@ class Native:
             ("cs_sim_begin", [sp, ctypes.c_float, vp]),
             ("cs_sim_final_check", [sp, vp]),
             ("cs_scan_argmax", [sp, vp]),
+            ("cs_select_kth_largest", [vp, ctypes.c_int64, ctypes.c_int64, vp, vp]),
             ("cs_xchg_wait", [sp, vp]),
             ("cs_fps_step_lanes", [sp, ctypes.c_int32, ctypes.c_uint32, vp]),
         ):
@@ -176,6 +184,9 @@ class Native:
 
     def xchg_wait(self, s: CsState, stream: int) -> None:
         self._check(self.lib.cs_xchg_wait(ctypes.byref(s), stream), "cs_xchg_wait")
+
+    def select_kth_largest(self, h: int, n: int, k: int, scratch: int, stream: int) -> None:
+        self._check(self.lib.cs_select_kth_largest(h, n, k, scratch, stream), "cs_select_kth_largest")
 
     def scan_argmax(self, s: CsState, stream: int) -> None:
         self._check(self.lib.cs_scan_argmax(ctypes.byref(s), stream), "cs_scan_argmax")

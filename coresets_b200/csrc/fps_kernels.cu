@@ -1377,6 +1377,95 @@ DevInfo device_info() {
     return info;
 }
 
+// ---- exact selection: k-th largest live entry of h ---------------------------------------------
+// Radix select over the bit patterns of the non-negative floats (monotone as unsigned integers;
+// -0.0 counts as 0), most significant byte first.  Each pass histograms the byte under the prefix
+// found so far; the last block to finish picks the bucket that holds the k-th largest.
+struct SelectCtl {
+    cs_select_result res;          // what the host reads
+    unsigned prefix;               // leading bytes of the answer found so far
+    unsigned k_rem;                // rank of the answer among the entries that share the prefix
+    unsigned ticket;
+    unsigned pad;
+    unsigned hist[4][256];
+};
+static_assert(sizeof(SelectCtl) <= CS_SELECT_SCRATCH_BYTES, "selection scratch");
+
+__global__ void select_init_kernel(SelectCtl* c, unsigned k) {
+    for (int i = threadIdx.x; i < 4 * 256; i += blockDim.x) (&c->hist[0][0])[i] = 0u;
+    if (threadIdx.x == 0) {
+        c->res.value = 0.0f;
+        c->res.valid = 0;
+        c->res.n_alive = 0;
+        c->prefix = 0u;
+        c->k_rem = k;
+        c->ticket = 0u;
+    }
+}
+
+template <int PASS>
+__global__ void __launch_bounds__(kThreads) select_pass_kernel(const float* __restrict__ h, const int64_t n, SelectCtl* c) {
+    __shared__ unsigned s_hist[256];
+    __shared__ int s_last;
+    s_hist[threadIdx.x] = 0u;                          // kThreads == 256
+    __syncthreads();
+    if (PASS > 0 && c->res.valid == 0 && c->k_rem == 0u) return;   // pass 0 found k out of range (uniform)
+    constexpr int shift = 24 - 8 * PASS;
+    constexpr unsigned hi_mask = PASS == 0 ? 0u : (0xffffffffu << (32 - 8 * PASS));
+    const unsigned prefix = c->prefix;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t base = (int64_t)blockIdx.x * blockDim.x; base < n; base += stride) {   // block-uniform trip count
+        const int64_t r = base + threadIdx.x;
+        const float v = r < n ? h[r] : -1.0f;
+        const bool alive = v >= 0.0f;                  // false for selected rows (-1) and NaN
+        const unsigned key = (v == 0.0f) ? 0u : __float_as_uint(v);
+        const bool hit = alive && ((key & hi_mask) == prefix);
+        const unsigned bin = (key >> shift) & 255u;
+        // one shared-memory atomic per distinct bin of the warp
+        const unsigned act = __ballot_sync(kFull, hit);
+        if (hit) {
+            const unsigned peers = __match_any_sync(act, bin);
+            if ((int)(__ffs(peers) - 1) == (int)(threadIdx.x & 31)) atomicAdd(&s_hist[bin], (unsigned)__popc(peers));
+        }
+    }
+    __syncthreads();
+    if (s_hist[threadIdx.x]) atomicAdd(&c->hist[PASS][threadIdx.x], s_hist[threadIdx.x]);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(&c->ticket, 1u) == gridDim.x - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) {
+        const volatile unsigned* hist = c->hist[PASS];
+        unsigned k = c->k_rem;
+        if (PASS == 0) {
+            unsigned long long total = 0;
+            for (int b = 0; b < 256; ++b) total += hist[b];
+            c->res.n_alive = (int64_t)total;
+            if (k == 0u || (unsigned long long)k > total) k = 0u;      // out of range: later passes do nothing
+        }
+        if (k != 0u) {
+            unsigned above = 0u;
+            int b = 255;
+            for (; b > 0; --b) {
+                const unsigned cnt = hist[b];
+                if (above + cnt >= k) break;
+                above += cnt;
+            }
+            c->prefix = prefix | ((unsigned)b << shift);
+            c->k_rem = k - above;
+            if (PASS == 3) {
+                c->res.value = __uint_as_float(c->prefix);
+                c->res.valid = 1;
+            }
+        } else {
+            c->k_rem = 0u;
+        }
+        c->ticket = 0u;
+    }
+}
+
 int check_launch() {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
@@ -1706,6 +1795,24 @@ int cs_scan_argmax(const cs_state* s, cs_stream stream) {
     int64_t lim = (int64_t)d.sms * 8;
     int grid = (int)(want < 1 ? 1 : (want < lim ? want : lim));
     scan_argmax_kernel<<<grid, kThreads, 0, st>>>(*s);
+    return check_launch();
+}
+
+int cs_select_kth_largest(const float* h, int64_t n, int64_t k, void* scratch, cs_stream stream) {
+    if (!scratch || n < 0 || n > 0x7fffffffLL || (n > 0 && !h)) return CS_E_ARG;
+    DevInfo d = device_info();
+    if (!d.ok) return CS_E_DEVICE;
+    cudaStream_t st = (cudaStream_t)stream;
+    SelectCtl* c = reinterpret_cast<SelectCtl*>(scratch);
+    const unsigned k32 = (k >= 1 && k <= n) ? (unsigned)k : 0u;       // 0 = out of range: only the count is produced
+    select_init_kernel<<<1, kThreads, 0, st>>>(c, k32);
+    int64_t want = (n + kThreads * 8 - 1) / (kThreads * 8);
+    int64_t cap = (int64_t)d.sms * 8;
+    const int grid = (int)(want < 1 ? 1 : (want < cap ? want : cap));
+    select_pass_kernel<0><<<grid, kThreads, 0, st>>>(h, n, c);
+    select_pass_kernel<1><<<grid, kThreads, 0, st>>>(h, n, c);
+    select_pass_kernel<2><<<grid, kThreads, 0, st>>>(h, n, c);
+    select_pass_kernel<3><<<grid, kThreads, 0, st>>>(h, n, c);
     return check_launch();
 }
 

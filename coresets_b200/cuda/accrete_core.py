@@ -430,18 +430,17 @@ class AccreteDriver:
             if n_start + mid + points_left >= N:
                 return True
             self._reconstruct(snap, added_t, sel_start_t, mid)
-            h_mid = self.S.h[: self.layout.N_shard]
-            alive = h_mid >= 0
-            n_pos = int(alive.sum().item())
+            # after a fill of points_left picks the coverage is at most the (points_left + 1)-th
+            # largest live h: the reference's kthvalue early exit (bisect.py:64-71) as one exact
+            # device-side selection (count and value in a single read-back)
+            cov_upper, n_pos = self.S.kth_largest_live(points_left + 1)
             if 0 < points_left < n_pos:
-                # after a fill of points_left picks the coverage is at most the k-th largest h
-                cov_upper = float(torch.kthvalue(h_mid[alive], n_pos - points_left).values.item())
                 if sep_mid > cov_upper:
                     return True
             elif points_left >= n_pos:
                 return True
             if points_left == 0:
-                return sep_mid > float(h_mid.max().item())
+                return sep_mid > cov_upper           # k = 1: the maximum of the live rows (bisect.py:78-80)
             ok, _ = self._simulate(float(sep_mid), points_left, n_start + mid)
             self._n_probe += 1
             return ok

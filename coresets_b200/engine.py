@@ -342,6 +342,27 @@ class ShardEngine:
         for e in engines:
             e._unconsumed = True
 
+    def kth_largest_live(self, k: int):
+        """``(value, n_alive)``: the exact ``k``-th largest entry of this engine's ``h`` among the
+        rows that are not selected (``h >= 0``) and how many such rows there are; ``value`` is
+        ``None`` when ``k`` is outside ``[1, n_alive]``.  Equals
+        ``torch.kthvalue(h[h >= 0], n_alive - k + 1)`` (cuda/_internal/bisect.py:64-71): a selection
+        returns one of its inputs.  One 16-byte read-back."""
+        if not hasattr(self, "_select_scratch"):
+            self._select_scratch = torch.zeros(_native.SELECT_SCRATCH_BYTES // 8, dtype=torch.int64, device=self.device)
+            self._select_host = torch.empty(2, dtype=torch.int64, pin_memory=self.on_cuda)
+        self.native.select_kth_largest(self.h.data_ptr(), self.N_local, int(k), self._select_scratch.data_ptr(),
+                                       self._stream())
+        if self.on_cuda:
+            self._select_host.copy_(self._select_scratch[:2], non_blocking=True)
+            torch.cuda.current_stream(self.device).synchronize()
+            src = self._select_host
+        else:
+            src = self._select_scratch
+        res = _native.SelectResult()
+        ctypes.memmove(ctypes.addressof(res), src.data_ptr(), ctypes.sizeof(res))
+        return (float(res.value) if res.valid else None), int(res.n_alive)
+
     # -- read-back -----------------------------------------------------------------------------------
     def read_ctl(self) -> CtlView:
         """Copy the control block to the host (synchronises the current stream)."""

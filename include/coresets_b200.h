@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define CS_ABI_VERSION 4
+#define CS_ABI_VERSION 5
 
 #if defined(__GNUC__)
 #define CS_API __attribute__((visibility("default")))
@@ -214,6 +214,23 @@ CS_API int cs_xchg_wait(const cs_state* s, cs_stream stream);
  * cuda/multi/sharded.py:112-131, 470-490 and kernels/simulate.cu:84, multi.cu:511-517.
  */
 CS_API int cs_scan_argmax(const cs_state* s, cs_stream stream);
+
+/*
+ * Exact k-th largest (k = 1 is the maximum) of the entries of h[0..n) that are >= 0, and how
+ * many such entries there are.  Selected rows carry h = -1 and do not count.  Replaces the
+ * `(h_mid >= 0).sum()` + `torch.kthvalue(h_mid[h_mid >= 0], rank)` pair of the bisect early exit
+ * (cuda/_internal/bisect.py:64-71; rank = n_alive - k + 1 there): a selection returns one of
+ * the inputs, so the value is the same float whatever algorithm finds it.  Four radix passes over
+ * h, no host synchronisation.  `scratch` is CS_SELECT_SCRATCH_BYTES of device memory owned by
+ * the caller; when the stream has run, its first bytes hold a cs_select_result.
+ */
+#define CS_SELECT_SCRATCH_BYTES 8192
+typedef struct cs_select_result {
+    float value;       /* the k-th largest live entry; undefined when valid == 0            */
+    int32_t valid;     /* 1 when 1 <= k <= n_alive                                           */
+    int64_t n_alive;   /* entries of h that are >= 0                                         */
+} cs_select_result;
+CS_API int cs_select_kth_largest(const float* h, int64_t n, int64_t k, void* scratch, cs_stream stream);
 
 /*
  * Several probes at once: `n_lanes` (1..8) independent states that share X / norms /

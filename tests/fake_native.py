@@ -191,6 +191,15 @@ class FakeNative:
         self._publish(s, a, k)
         ctl.n_sel = i + 1
 
+    def select_kth_largest(self, h_ptr, n, k, scratch_ptr, stream):
+        from coresets_b200._native import SelectResult
+        h = _view(h_ptr, n, np.float32)
+        alive = np.sort(h[h >= 0])
+        res = SelectResult.from_address(scratch_ptr)
+        res.n_alive = int(alive.size)
+        res.valid = 1 if 1 <= k <= alive.size else 0
+        res.value = float(alive[alive.size - k]) if res.valid else 0.0
+
     def scan_argmax(self, s, stream):
         a = self._arrays(s)
         ctl = self._ctl(s)

@@ -476,3 +476,36 @@ def test_more_centres_than_the_shared_bound_table():
     X = gaussian_mixture(N, D, 8, seed=77)
     eng, norms = run_engine(X, k)
     assert_matches_oracle(eng, X, norms, k)
+
+
+# ---- exact selection (the bisect early exit of the single-GPU accretion driver) -------------------
+@pytest.mark.parametrize("n", [1, 2, 255, 4096, 100_003, 3_000_000])
+def test_kth_largest_live_matches_a_sort(n):
+    """cs_select_kth_largest against torch.sort / torch.kthvalue on h with selected rows (-1),
+    zeros of both signs, duplicates, +inf and a wide range of magnitudes."""
+    g = torch.Generator(device="cpu").manual_seed(n)
+    h = torch.rand(n, generator=g) ** 4 * 1e4
+    h[torch.rand(n, generator=g) < 0.2] = -1.0                  # selected rows
+    h[torch.rand(n, generator=g) < 0.05] = 0.0
+    h[torch.rand(n, generator=g) < 0.02] = -0.0
+    h[torch.rand(n, generator=g) < 0.1] = 3.25                  # heavy duplicates
+    if n > 10:
+        h[7] = float("inf")
+        h[3] = 1e-30
+    dev = torch.device("cuda:0")
+    X = torch.zeros((n, 4), device=dev)
+    eng = engine.ShardEngine(X, torch.zeros(n, device=dev), 1)
+    eng.h.copy_(h.to(dev))
+    live = torch.sort(h[h >= 0]).values
+    n_alive = int(live.numel())
+    ks = sorted({1, 2, 3, n_alive // 2, n_alive - 1, n_alive, n_alive + 1, 0, 17, 1000} )
+    for k in ks:
+        val, cnt = eng.kth_largest_live(k)
+        assert cnt == n_alive
+        if 1 <= k <= n_alive:
+            want = float(live[n_alive - k])
+            assert val == want, (k, val, want)
+            if n_alive - k + 1 >= 1:
+                assert val == float(torch.kthvalue(h[h >= 0], n_alive - k + 1).values)
+        else:
+            assert val is None
