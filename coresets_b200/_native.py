@@ -13,7 +13,7 @@ from typing import Optional
 
 from . import build as _build
 
-CS_ABI_VERSION = 5
+CS_ABI_VERSION = 6
 SELECT_SCRATCH_BYTES = 8192
 F_ELEMENT_ORDER = 1
 CS_CTL_BYTES = 256
@@ -33,7 +33,7 @@ EXPORTS = (
     "cs_version", "cs_error_string", "cs_last_cuda_error", "cs_device_check", "cs_init_state",
     "cs_reset_ctl", "cs_force_pick", "cs_commit_bound", "cs_fps_step", "cs_sim_begin",
     "cs_sim_final_check", "cs_xchg_window_words", "cs_xchg_wait", "cs_scan_argmax", "cs_fps_step_lanes", "cs_fps_step_noalloc",
-    "cs_select_kth_largest",
+    "cs_select_kth_largest", "cs_pool_argmax",
 )
 
 
@@ -63,6 +63,18 @@ class CsState(ctypes.Structure):
         ("xchg_timeout_ms", ctypes.c_int32),
         ("flags", ctypes.c_int32),
     ]
+
+
+def decode_key(key: int):
+    """``(value, global index)`` of a 64-bit arg-max key (include/coresets_b200.h, cs_pool_argmax);
+    ``(-inf, -1)`` for key 0."""
+    import struct
+    key &= 0xFFFFFFFFFFFFFFFF
+    if key == 0:
+        return float("-inf"), -1
+    o = key >> 32
+    b = (o & 0x7FFFFFFF) if o & 0x80000000 else (~o) & 0xFFFFFFFF
+    return struct.unpack("<f", struct.pack("<I", b))[0], 0xFFFFFFFF - (key & 0xFFFFFFFF)
 
 
 class SelectResult(ctypes.Structure):
@@ -128,6 +140,7 @@ class Native:
             ("cs_sim_final_check", [sp, vp]),
             ("cs_scan_argmax", [sp, vp]),
             ("cs_select_kth_largest", [vp, ctypes.c_int64, ctypes.c_int64, vp, vp]),
+            ("cs_pool_argmax", [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, vp, vp]),
             ("cs_xchg_wait", [sp, vp]),
             ("cs_fps_step_lanes", [sp, ctypes.c_int32, ctypes.c_uint32, vp]),
         ):
@@ -184,6 +197,10 @@ class Native:
 
     def xchg_wait(self, s: CsState, stream: int) -> None:
         self._check(self.lib.cs_xchg_wait(ctypes.byref(s), stream), "cs_xchg_wait")
+
+    def pool_argmax(self, h: int, pool: int, n_pool: int, shard_offset: int, n_local: int, out_key: int,
+                    stream: int) -> None:
+        self._check(self.lib.cs_pool_argmax(h, pool, n_pool, shard_offset, n_local, out_key, stream), "cs_pool_argmax")
 
     def select_kth_largest(self, h: int, n: int, k: int, scratch: int, stream: int) -> None:
         self._check(self.lib.cs_select_kth_largest(h, n, k, scratch, stream), "cs_select_kth_largest")

@@ -1466,6 +1466,31 @@ __global__ void __launch_bounds__(kThreads) select_pass_kernel(const float* __re
     }
 }
 
+// ---- arg-max of h over a list of rows (accretion forward loop) --------------------------------
+__global__ void __launch_bounds__(kThreads) pool_argmax_kernel(const float* __restrict__ h, const int64_t* __restrict__ pool,
+                                                               const int64_t n_pool, const int64_t lo, const int64_t n_local,
+                                                               u64* out_key) {
+    __shared__ u64 s_keys[kWarps];
+    u64 best = 0;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n_pool; j += stride) {
+        const int64_t p = pool[j];
+        if (p >= lo && p < lo + n_local) {
+            const u64 k = make_key(h[p - lo], p);
+            best = k > best ? k : best;
+        }
+    }
+    best = warp_max_key(best);
+    if ((threadIdx.x & 31) == 0) s_keys[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        u64 bk = 0;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) bk = s_keys[w] > bk ? s_keys[w] : bk;
+        if (bk) atomicMax(out_key, bk);
+    }
+}
+
 int check_launch() {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
@@ -1795,6 +1820,21 @@ int cs_scan_argmax(const cs_state* s, cs_stream stream) {
     int64_t lim = (int64_t)d.sms * 8;
     int grid = (int)(want < 1 ? 1 : (want < lim ? want : lim));
     scan_argmax_kernel<<<grid, kThreads, 0, st>>>(*s);
+    return check_launch();
+}
+
+int cs_pool_argmax(const float* h, const int64_t* pool, int64_t n_pool, int64_t shard_offset, int64_t n_local,
+                   uint64_t* out_key, cs_stream stream) {
+    if (!out_key || n_pool < 0 || n_local < 0 || (n_pool > 0 && !pool) || (n_local > 0 && !h)) return CS_E_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemsetAsync(out_key, 0, sizeof(uint64_t), st) != cudaSuccess) {
+        g_last_cuda = cudaGetLastError();
+        return CS_E_LAUNCH;
+    }
+    if (n_pool == 0 || n_local == 0) return CS_OK;
+    int64_t want = (n_pool + kThreads - 1) / kThreads;
+    const int grid = (int)(want > 1024 ? 1024 : want);
+    pool_argmax_kernel<<<grid, kThreads, 0, st>>>(h, pool, n_pool, shard_offset, n_local, reinterpret_cast<u64*>(out_key));
     return check_launch();
 }
 

@@ -29,7 +29,7 @@ import torch.distributed as dist
 from torch import Tensor
 
 from .. import engine as _engine
-from .._native import RULE_NONE, RULE_SIM_SHARDED, RULE_SIM_SINGLE
+from .._native import RULE_NONE, RULE_SIM_SHARDED, RULE_SIM_SINGLE, decode_key
 from . import search
 from .diag import PhaseTimer, Tracer, fmt_gap, invariant_numbers, level_counts
 from .multi.layout import ShardLayout
@@ -138,21 +138,30 @@ class AccreteDriver:
         self._key_valid = True
 
     def _restricted_argmax(self, pool: Tensor) -> Tuple[float, int]:
-        """Largest ``h`` over the global indices in ``pool`` (sorted), ties to the smallest index
-        (block_forward.py:38-53, sharded.py:174-210)."""
-        lo, n = self.layout.shard_offset, self.layout.N_shard
-        local = pool[(pool >= lo) & (pool < lo + n)] if self.multi else pool
-        pair = torch.tensor([float("-inf"), -1.0], dtype=torch.float64, device=self.device)
-        if local.numel() > 0:
-            h_local = self.E.h[local - lo]
-            best = h_local.max()
-            pair[0] = best.double()
-            pair[1] = local[h_local == best].min().double()
+        """Largest ``h`` over the global indices in ``pool``, ties to the smallest index
+        (block_forward.py:38-53, sharded.py:174-210): one kernel reduces this shard's part to a
+        64-bit key (value, then smaller index), the ranks' keys are gathered, one read-back.
+        Rows of the pool that are already selected carry ``h = -1`` and can only win when nothing
+        else is left, which the caller reads as "dry" exactly like an empty pool."""
+        E = self.E
+        if not hasattr(self, "_pool_key"):
+            world = self.layout.world_size if self.multi else 1
+            self._pool_key = torch.zeros(1, dtype=torch.int64, device=self.device)
+            self._pool_keys = torch.zeros(world, dtype=torch.int64, device=self.device)
+            self._pool_host = torch.empty(world, dtype=torch.int64, pin_memory=E.on_cuda)
+        E.native.pool_argmax(E.h.data_ptr(), pool.data_ptr(), int(pool.numel()), self.layout.shard_offset,
+                             self.layout.N_shard, self._pool_key.data_ptr(), E._stream())
+        src = self._pool_key
         if self.multi:
-            allp = torch.empty((self.layout.world_size, 2), dtype=torch.float64, device=self.device)
-            dist.all_gather_into_tensor(allp.view(-1), pair)
-            pair = allp[torch.argmax(allp[:, 0])]      # first maximum = lowest rank = smallest index
-        val, idx = pair.tolist()
+            dist.all_gather_into_tensor(self._pool_keys, self._pool_key)
+            src = self._pool_keys
+        if E.on_cuda:
+            self._pool_host[: src.numel()].copy_(src, non_blocking=True)
+            torch.cuda.current_stream(self.device).synchronize()
+            keys = self._pool_host[: src.numel()].tolist()
+        else:
+            keys = src.tolist()
+        val, idx = decode_key(max(k & 0xFFFFFFFFFFFFFFFF for k in keys))
         return float(val), int(idx)
 
     def _global_max(self, h: Tensor) -> float:

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define CS_ABI_VERSION 5
+#define CS_ABI_VERSION 6
 
 #if defined(__GNUC__)
 #define CS_API __attribute__((visibility("default")))
@@ -231,6 +231,19 @@ typedef struct cs_select_result {
     int64_t n_alive;   /* entries of h that are >= 0                                         */
 } cs_select_result;
 CS_API int cs_select_kth_largest(const float* h, int64_t n, int64_t k, void* scratch, cs_stream stream);
+
+/*
+ * Arg-max of h restricted to a list of global row indices: *out_key (device, 8 bytes) becomes the
+ * largest key(h[p - shard_offset], p) over the entries p of `pool` that this shard owns, 0 when it
+ * owns none.  A key orders by value, then by SMALLER index, and decodes as
+ *   value = bits(key >> 32) mapped back (sign-magnitude to two's-complement order),
+ *   index = 0xFFFFFFFF - (key & 0xFFFFFFFF);
+ * the maximum over the ranks' keys is the global winner.  Replaces the masked gather / max /
+ * min-index sequence of the accretion forward loop (cuda/_internal/block_forward.py:38-53,
+ * cuda/multi/sharded.py:174-210).
+ */
+CS_API int cs_pool_argmax(const float* h, const int64_t* pool, int64_t n_pool, int64_t shard_offset,
+                          int64_t n_local, uint64_t* out_key, cs_stream stream);
 
 /*
  * Several probes at once: `n_lanes` (1..8) independent states that share X / norms /

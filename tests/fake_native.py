@@ -191,6 +191,14 @@ class FakeNative:
         self._publish(s, a, k)
         ctl.n_sel = i + 1
 
+    def pool_argmax(self, h_ptr, pool_ptr, n_pool, shard_offset, n_local, out_ptr, stream):
+        h = _view(h_ptr, n_local, np.float32)
+        pool = _view(pool_ptr, n_pool, np.int64)
+        best = 0
+        for p in pool[(pool >= shard_offset) & (pool < shard_offset + n_local)]:
+            best = max(best, make_key(h[p - shard_offset], int(p)))
+        ctypes.c_uint64.from_address(out_ptr).value = best
+
     def select_kth_largest(self, h_ptr, n, k, scratch_ptr, stream):
         from coresets_b200._native import SelectResult
         h = _view(h_ptr, n, np.float32)
