@@ -34,3 +34,20 @@ def test_struct_layouts_match_the_header():
     assert ctypes.sizeof(_native.CsState) == 128 + 8 + 64 + 8  # + rank/xchg, 8 peer windows, timeout
     assert _native.CsState.D.offset == 48 and _native.CsState.world_size.offset == 52
     assert _native.CtlView.live_rows.offset == 40 and _native.CtlView.last_idx.offset == 52
+
+
+def test_decode_key_round_trip():
+    """The Python decoder of the 64-bit arg-max key against the encoder of the test stand-in."""
+    from tests.fake_native import make_key
+    import numpy as np
+    assert _native.decode_key(0) == (float("-inf"), -1)
+    for h in (0.0, 1e-30, 3.25, 1e9, float("inf"), -1.0):
+        for idx in (0, 1, 12345, 2**31 - 1):
+            val, i = _native.decode_key(make_key(np.float32(h), idx))
+            assert i == idx and np.float32(val) == np.float32(h)
+    # order: larger value first, then the smaller index
+    assert make_key(np.float32(2.0), 9) > make_key(np.float32(1.0), 3)
+    assert make_key(np.float32(2.0), 3) > make_key(np.float32(2.0), 9)
+    # a key read back as a signed 64-bit integer decodes the same
+    k = make_key(np.float32(5.0), 77)
+    assert _native.decode_key(k - (1 << 64)) == (5.0, 77)
