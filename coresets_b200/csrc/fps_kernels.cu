@@ -832,53 +832,16 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_queue_kernel
 // (cp.async.bulk, the 1-D TMA path: rows are contiguous, no tensor map needed) into a ring of
 // shared-memory stages, with the copies of several stages in flight while the consumer warps work:
 // memory-level parallelism no longer depends on registers or occupancy.  One producer warp issues
-// the copies and arms the "full" mbarriers with the byte count; eight consumer warps wait on
+// the copies and arms the "full" mbarriers with the byte count; the consumer warps wait on
 // "full", take their rows of the tile from shared memory (512-byte conflict-free reads), run the
 // same per-row arithmetic as fps_step_kernel, and release the stage through the "empty" mbarrier.
 // Every wait is bounded; a wait that runs out sets status = 4 and the block drains and leaves.
-// Ring shapes per row width, found by measurement on B200 (stages S, resident blocks per SM B,
-// bytes of X per stage T, consumer warps W): one block per SM with 160-200 KB of copies in flight;
-// narrow rows need sixteen consumer warps to keep up with the ring.
-#ifndef CS_TMA_NARROW_S
-#define CS_TMA_NARROW_S 3
-#endif
-#ifndef CS_TMA_NARROW_B
-#define CS_TMA_NARROW_B 1
-#endif
-#ifndef CS_TMA_NARROW_T
-#define CS_TMA_NARROW_T 65536
-#endif
-#ifndef CS_TMA_NARROW_W
-#define CS_TMA_NARROW_W 16
-#endif
-#ifndef CS_TMA_MID_S
-#define CS_TMA_MID_S 3
-#endif
-#ifndef CS_TMA_MID_B
-#define CS_TMA_MID_B 1
-#endif
-#ifndef CS_TMA_MID_T
-#define CS_TMA_MID_T 65536
-#endif
-#ifndef CS_TMA_MID_W
-#define CS_TMA_MID_W 8
-#endif
-#ifndef CS_TMA_WIDE_S
-#define CS_TMA_WIDE_S 5
-#endif
-#ifndef CS_TMA_WIDE_B
-#define CS_TMA_WIDE_B 1
-#endif
-#ifndef CS_TMA_WIDE_T
-#define CS_TMA_WIDE_T 40960
-#endif
-#ifndef CS_TMA_WIDE_W
-#define CS_TMA_WIDE_W 8
-#endif
-struct RingCfg { int stages, blocks, tile_bytes, warps; };
-constexpr RingCfg kRingNarrow{CS_TMA_NARROW_S, CS_TMA_NARROW_B, CS_TMA_NARROW_T, CS_TMA_NARROW_W};   // D <= 64
-constexpr RingCfg kRingMid{CS_TMA_MID_S, CS_TMA_MID_B, CS_TMA_MID_T, CS_TMA_MID_W};                  // 64 < D <= 128
-constexpr RingCfg kRingWide{CS_TMA_WIDE_S, CS_TMA_WIDE_B, CS_TMA_WIDE_T, CS_TMA_WIDE_W};             // 128 < D <= 1024
+// Ring shapes per row width, found by measurement on B200: one block per SM with 160-200 KB of
+// copies in flight; narrow rows need sixteen consumer warps to keep up with the ring.
+struct RingCfg { int stages, blocks, tile_bytes, warps; };   // stages, blocks per SM, bytes of X per stage, consumer warps
+constexpr RingCfg kRingNarrow{3, 1, 65536, 16};   // D <= 64
+constexpr RingCfg kRingMid{3, 1, 65536, 8};       // 64 < D <= 128
+constexpr RingCfg kRingWide{5, 1, 40960, 8};      // 128 < D <= 1024
 constexpr int kTmaMaxWarps = 16;
 constexpr int kSpinLimit = 1 << 22;
 
