@@ -1820,7 +1820,8 @@ int cs_select_kth_largest(const float* h, int64_t n, int64_t k, void* scratch, c
 }
 
 int cs_fps_step_lanes(const cs_state* lanes, int32_t n_lanes, uint32_t mode, cs_stream stream) {
-    if (!lanes || n_lanes < 1 || n_lanes > CS_MAX_LANES || mode > CS_MODE_DENSE) return CS_E_ARG;
+    if (!lanes || n_lanes < 1 || n_lanes > CS_MAX_LANES) return CS_E_ARG;
+    if (mode != CS_MODE_PRUNE && mode != CS_MODE_DENSE && mode != CS_MODE_PRUNE_INLINE) return CS_E_ARG;
     for (int l = 0; l < n_lanes; ++l) {
         int rc = validate(&lanes[l]);
         if (rc) return rc;
@@ -1829,8 +1830,13 @@ int cs_fps_step_lanes(const cs_state* lanes, int32_t n_lanes, uint32_t mode, cs_
             return CS_E_ARG;                   // lanes share the matrix; only their state differs
     }
     const int D = lanes[0].D;
-    // one lane, rows that are not 16-byte chunks, or very wide rows: the single-state kernel per lane
-    if (n_lanes == 1 || (lanes[0].flags & CS_F_ELEMENT_ORDER) || (D & 3) != 0 || D > 1024 || lanes[0].N_local == 0) {
+    // Default prune mode: one deferred-row step per lane.  Sharing the pass over X pays when most
+    // rows are read (dense mode); in prune mode the rows are a minor part of the traffic and the
+    // per-lane kernel is several times faster than the fused walk (measured 0.43 ms against
+    // 1.62 ms per lock-step pick of four lanes on 37.5 M x 128).
+    // Also per lane: one lane, rows that are not 16-byte chunks, very wide rows.
+    if (mode == CS_MODE_PRUNE || n_lanes == 1 || (lanes[0].flags & CS_F_ELEMENT_ORDER) || (D & 3) != 0 || D > 1024 ||
+        lanes[0].N_local == 0) {
         for (int l = 0; l < n_lanes; ++l) {
             int rc = cs_fps_step(&lanes[l], mode, stream);
             if (rc) return rc;

@@ -248,7 +248,9 @@ CS_API int cs_pool_argmax(const float* h, const int64_t* pool, int64_t n_pool, i
 /*
  * Several probes at once: `n_lanes` (1..8) independent states that share X / norms /
  * N_local / D / shard_offset / world_size but own their h, voronoi, centres and control
- * block.  One pass over X serves every lane; each lane's arithmetic is that of cs_fps_step.
+ * block.  Each lane's arithmetic is that of cs_fps_step.  CS_MODE_DENSE and
+ * CS_MODE_PRUNE_INLINE serve every lane from ONE pass over X; CS_MODE_PRUNE runs one
+ * deferred-row step per lane, which is faster when few rows pass the triangle test.
  * Replaces voronoi_update_lanes_kernel (kernels/multi.cu:569-708).
  */
 CS_API int cs_fps_step_lanes(const cs_state* lanes, int32_t n_lanes, uint32_t mode, cs_stream stream);

@@ -435,10 +435,14 @@ def test_peer_exchange_wait_times_out_with_a_status(monkeypatch):
 # ---- fused multi-state step ("lanes") -------------------------------------------------------------
 @pytest.mark.parametrize("N,D,L", [(5000, 128, 4), (3001, 64, 2), (2000, 256, 3), (1500, 1024, 2), (4000, 32, 8),
                                    (900, 50, 3)])
-def test_lanes_step_equals_separate_steps(N, D, L):
-    """L states with different histories share X: one fused pass must leave every state exactly
-    where its own cs_fps_step leaves it (h bits, voronoi, next key, pick counter), several steps
-    in a row."""
+@pytest.mark.parametrize("lane_mode", ["prune", "inline", "dense"])
+def test_lanes_step_equals_separate_steps(N, D, L, lane_mode):
+    """L states with different histories share X: one cs_fps_step_lanes call (per-lane deferred-row
+    steps in prune mode, ONE fused pass over X in the inline and dense modes) must leave every
+    state exactly where its own cs_fps_step leaves it (h bits, voronoi, next key, pick counter),
+    several steps in a row."""
+    from coresets_b200._native import MODE_PRUNE_INLINE
+    lanes_mode = {"prune": MODE_PRUNE, "inline": MODE_PRUNE_INLINE, "dense": MODE_DENSE}[lane_mode]
     dev = torch.device("cuda:0")
     X = torch.from_numpy(gaussian_mixture(N, D, 8, seed=N + D + L)).to(dev)
     norms = engine.row_norms(X)
@@ -457,7 +461,7 @@ def test_lanes_step_equals_separate_steps(N, D, L):
     for _ in range(5):
         for e in fused:
             e.exchange(); e.commit()
-        engine.ShardEngine.step_lanes(fused)
+        engine.ShardEngine.step_lanes(fused, mode=lanes_mode)
         for e in apart:
             e.exchange(); e.commit(); e.step()
         for a, b in zip(fused, apart):
