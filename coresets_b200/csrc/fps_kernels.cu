@@ -596,10 +596,13 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
 constexpr int kQueueCap = 160;           // a batch remainder (< 16) plus one super-tile (128), padded
 
 template <int CPL, bool FULL, bool HALF>
-__global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_queue_kernel(const cs_state s, const int n_bound_smem) {
+__global__ void __launch_bounds__(kThreads, CPL == 0 ? 2 : CS_MIN_BLOCKS) fps_step_queue_kernel(const cs_state s, const int n_bound_smem) {
     static_assert(kRowsPerLane == 4, "the deferred-row kernel reads four rows per lane");
-    extern __shared__ __align__(16) float s_dyn[];               // the first n_bound_smem triangle bounds
+    // dynamic shared memory: the first n_bound_smem triangle bounds, then (CPL == 0, the path for
+    // any row width and for the element-wise summation order) the centre
+    extern __shared__ __align__(16) float s_dyn[];
     float* s_dsl = s_dyn;
+    float* s_cen = s_dyn + n_bound_smem;
     __shared__ int2 s_queue[kWarps][kQueueCap];                  // (local row, bits of its h)
     __shared__ u64 s_keys[kWarps];
     __shared__ unsigned s_live[kWarps];
@@ -617,13 +620,18 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_queue_kernel
     const bool hi = HALF && lane >= 16;
     const bool first = (i == 0);
     const float nn = s.norms_sel[i];
-    float4 cen[CPL];
-    {
+    float4 cen[CPL ? CPL : 1];
+    if (CPL) {
         const float4* c4 = reinterpret_cast<const float4*>(s.X_sel + (int64_t)i * D);
 #pragma unroll
-        for (int c = 0; c < CPL; ++c)
+        for (int c = 0; c < (CPL ? CPL : 1); ++c)
             cen[c] = (FULL || sub + 32 * c < d4) ? c4[sub + 32 * c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+        const float* cen_g = s.X_sel + (int64_t)i * D;
+        for (int c = threadIdx.x; c < D; c += blockDim.x) s_cen[c] = cen_g[c];
     }
+    // chunked order needs whole 16-byte chunks and is what float32 inputs get (_shared.cuh:41-50)
+    const bool chunked = (D & 3) == 0 && !(s.flags & CS_F_ELEMENT_ORDER);
     const int nb = i < n_bound_smem ? i : n_bound_smem;
     // voronoi <= i (the row committed for this pick carries i itself), so with i inside the staged
     // table every look-up stays within the block's shared memory
@@ -644,12 +652,49 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_queue_kernel
     unsigned live_cnt = 0;
     int2* q = s_queue[warp];
     int qn = 0;                                                  // entries waiting (warp-uniform)
-    constexpr int BS = HALF ? 16 : (CPL >= 8 ? 1 : 8 / CPL);     // rows of a batch
+    constexpr int BS = HALF ? 16 : (CPL == 0 ? 4 : (CPL >= 8 ? 1 : 8 / CPL));     // rows of a batch
 
     // ---- one batch: entries q[base .. base+cnt), cnt <= BS; lane b < cnt finishes entry b --------
     auto run_batch = [&](const int base, const int cnt) {
         float mydot = 0.0f;
-        if (HALF) {
+        if (CPL == 0) {
+            // any row width: the lanes stride over the row, four rows side by side
+            int rows[4];
+            float acc[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                rows[b] = q[base + (b < cnt ? b : cnt - 1)].x;
+                acc[b] = 0.0f;
+            }
+            if (chunked) {
+                const float4* c4 = reinterpret_cast<const float4*>(s_cen);
+#pragma unroll 2
+                for (int c = lane; c < d4; c += 32) {
+                    const float4 cc = c4[c];
+                    float4 a[4];
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) a[b] = ld_stream4(X4 + (int64_t)rows[b] * d4 + c);
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) acc[b] = __fadd_rn(acc[b], chunk_dot(a[b], cc));
+                }
+            } else {
+#pragma unroll 2
+                for (int c = lane; c < D; c += 32) {                 // _shared.cuh:52-58: one fma per element
+                    float a[4];
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) a[b] = __ldcs(s.X + (int64_t)rows[b] * D + c);
+                    const float cc = s_cen[c];
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) acc[b] = __fmaf_rn(a[b], cc, acc[b]);
+                }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const float p = warp_tree_sum(acc[b]);
+                if (lane == b) mydot = p;
+            }
+        } else if (HALF) {
             float4 a[8];
 #pragma unroll
             for (int b = 0; b < 8; ++b) {
@@ -670,20 +715,20 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_queue_kernel
                 if (lane == 2 * b + 1) mydot = pb;
             }
         } else {
-            float4 a[BS][CPL];
+            float4 a[BS][CPL ? CPL : 1];
 #pragma unroll
             for (int b = 0; b < BS; ++b) {
                 const int r = q[base + (b < cnt ? b : cnt - 1)].x;
                 const float4* rp = X4 + (int64_t)r * d4;
 #pragma unroll
-                for (int c = 0; c < CPL; ++c)
+                for (int c = 0; c < (CPL ? CPL : 1); ++c)
                     a[b][c] = ld_stream4(rp + ((FULL || lane + 32 * c < d4) ? lane + 32 * c : 0));
             }
 #pragma unroll
             for (int b = 0; b < BS; ++b) {
                 float p = 0.0f;
 #pragma unroll
-                for (int c = 0; c < CPL; ++c)
+                for (int c = 0; c < (CPL ? CPL : 1); ++c)
                     if (FULL || lane + 32 * c < d4) p = __fadd_rn(p, chunk_dot(a[b][c], cen[c]));
                 p = warp_tree_sum(p);
                 if (lane == b) mydot = p;
@@ -1549,7 +1594,7 @@ int launch_step_queue(const cs_state* s, cudaStream_t st, int sms) {
     static thread_local size_t attr_set = 0, occ_smem = ~(size_t)0;
     static thread_local int occ_blocks = 0;
     const int n_bound = (int)(s->cap < kBoundSmemMax ? s->cap : kBoundSmemMax);
-    const size_t smem = (size_t)n_bound * sizeof(float);
+    const size_t smem = (size_t)n_bound * sizeof(float) + (CPL ? 0 : (size_t)s->D * sizeof(float));
     if (smem > 32 * 1024 && smem > attr_set) {
         if (cudaFuncSetAttribute(fps_step_queue_kernel<CPL, FULL, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) {
@@ -1715,7 +1760,9 @@ int cs_fps_step(const cs_state* s, uint32_t mode, cs_stream stream) {
         if (D <= 512) return launch_step_tma<4, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d.sms);
         return launch_step_tma<8, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d.sms);
     }
-    if (element_order || (D & 3) != 0 || D > 1024) return launch_step<0, false>(s, mode, st, d.sms);
+    const bool generic = element_order || (D & 3) != 0 || D > 1024;
+    if (generic && mode == CS_MODE_PRUNE && s->N_local > 0 && D <= 16384) return launch_step_queue<0, false>(s, st, d.sms);
+    if (generic) return launch_step<0, false>(s, mode, st, d.sms);
     if (mode == CS_MODE_PRUNE && s->N_local > 0) {
         switch (D) {
             case 128: return launch_step_queue<1, true>(s, st, d.sms);

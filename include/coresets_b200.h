@@ -51,8 +51,7 @@ extern "C" {
 /* cs_fps_step flags */
 #define CS_MODE_PRUNE 0u   /* rows excluded by the triangle bound are not loaded (default); the rows
                               that remain are queued and evaluated in batches */
-#define CS_MODE_PRUNE_INLINE 2u /* prune mode evaluating each remaining row where the scan meets it
-                              (the path rows of other widths take) */
+#define CS_MODE_PRUNE_INLINE 2u /* prune mode evaluating each remaining row where the scan meets it */
 #define CS_MODE_DENSE 1u   /* every live row's distance is computed; the bound only masks the
                               update, so results are identical to CS_MODE_PRUNE; X is streamed by
                               bulk asynchronous (TMA) copies when D % 4 == 0 and 32 <= D <= 1024 */
