@@ -354,12 +354,24 @@ class HostMatrix:
     RING_BYTES = 64 << 20
     RING_SLOTS = 8
 
-    def __init__(self, X: torch.Tensor):
+    def __init__(self, X: torch.Tensor, try_pinned: bool = False):
+        """``try_pinned``: keep the rows in page-locked memory outright (one DMA, no staging copy)
+        when the allocation succeeds; used when the matrix is a small part of the host's memory."""
         self.shape, self.dtype = tuple(X.shape), X.dtype
         self.pinned = False
-        self.host = torch.empty(self.shape, dtype=self.dtype)
+        self.host = None
+        if try_pinned:
+            try:
+                self.host = torch.empty(self.shape, dtype=self.dtype, pin_memory=True)
+                self.pinned = True
+            except RuntimeError:
+                torch.cuda.synchronize(X.device)
+                self.host = None
+        if self.host is None:
+            self.host = torch.empty(self.shape, dtype=self.dtype)
         rows = max(1, self.RING_BYTES // max(1, self.shape[1] * 4))
-        self.ring = [torch.empty((rows, self.shape[1]), dtype=self.dtype, pin_memory=True) for _ in range(self.RING_SLOTS)]
+        self.ring = [] if self.pinned else [torch.empty((rows, self.shape[1]), dtype=self.dtype, pin_memory=True)
+                                            for _ in range(self.RING_SLOTS)]
         self._move(X, to_device=False)
 
     def _move(self, X: torch.Tensor, to_device: bool) -> None:
@@ -436,7 +448,13 @@ def run_e2e(args, X, w, world, rank, device, K, W, off):
                 "skipped": f"host memory: {nbytes/1e9:.1f} GB per rank needed, {avail/1e9:.1f} GB available"}
     # torchrun pins OMP_NUM_THREADS=1; the pageable -> page-locked copies want this rank's share of the cores
     torch.set_num_threads(max(1, (os.cpu_count() or 1) // share))
-    hm = HostMatrix(X)
+    # Page-lock the rows outright when all ranks' matrices together are a small part of the host's
+    # memory (the 8-GPU split of the headline config on a 1 TB host); otherwise stage.  A single
+    # page-locked allocation of 96 GB failed on the 196 GB single-GPU host, 48 GB worked.
+    pin = torch.tensor([1 if (nbytes <= (40 << 30) and nbytes * share <= 0.2 * avail) else 0], device=device)
+    if world > 1:
+        dist.all_reduce(pin, op=dist.ReduceOp.MIN)
+    hm = HostMatrix(X, try_pinned=bool(int(pin.item())))
     torch.cuda.synchronize(device)
     sel_host = torch.empty(1 + W + K, dtype=torch.int64, pin_memory=True)
     eps_host = torch.empty(1 + W + K, dtype=torch.float32, pin_memory=True)
