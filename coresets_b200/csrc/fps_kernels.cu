@@ -406,7 +406,7 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
     // then a shared-memory read instead of an L2 round trip), then the centre on the generic path
     extern __shared__ __align__(16) float s_dyn[];
     float* s_dsl = s_dyn;
-    float* s_cen = s_dyn + n_bound_smem;
+    float* s_cen = s_dyn + ((n_bound_smem + 3) & ~3);            // 16-byte aligned: read as float4 chunks
     __shared__ u64 s_keys[kWarps];
     __shared__ unsigned s_live[kWarps];
     __shared__ int s_last;
@@ -589,20 +589,32 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
 // In prune mode few rows pass the triangle test and they are scattered, so walking them where
 // they are met leaves a warp with one or two row loads in flight and a long dependent chain per
 // super-tile.  Here the scan and the distance work are decoupled: a warp streams h / voronoi of
-// its super-tiles (the next one is already in flight), applies the test, and pushes the rows that
+// its super-tiles (four of them in flight through asynchronous copies), applies the test, and pushes the rows that
 // need a distance onto a warp-private queue in shared memory; whenever the queue holds a full
 // batch, the batch is evaluated branch-free with all of its row loads in flight.  The arithmetic
 // per row, the update rule and the arg-max order are those of fps_step_kernel, so the bits match.
 constexpr int kQueueCap = 160;           // a batch remainder (< 16) plus one super-tile (128), padded
+constexpr int kScanDepth = 4;            // super-tiles of h / voronoi in flight per warp (cp.async ring; 3-4 measured best)
+constexpr int kScanRingFloats = kWarps * kScanDepth * 256;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <int CPL, bool FULL, bool HALF>
 __global__ void __launch_bounds__(kThreads, CPL == 0 ? 2 : CS_MIN_BLOCKS) fps_step_queue_kernel(const cs_state s, const int n_bound_smem) {
     static_assert(kRowsPerLane == 4, "the deferred-row kernel reads four rows per lane");
-    // dynamic shared memory: the first n_bound_smem triangle bounds, then (CPL == 0, the path for
-    // any row width and for the element-wise summation order) the centre
+    // dynamic shared memory: the scan ring (per warp and slot 128 h, then 128 voronoi words), the
+    // first n_bound_smem triangle bounds, then (CPL == 0, the path for any row width and for the
+    // element-wise summation order) the centre
     extern __shared__ __align__(16) float s_dyn[];
-    float* s_dsl = s_dyn;
-    float* s_cen = s_dyn + n_bound_smem;
+    float (*s_ring)[kScanDepth][256] = reinterpret_cast<float (*)[kScanDepth][256]>(s_dyn);
+    float* s_dsl = s_dyn + kScanRingFloats;
+    float* s_cen = s_dsl + ((n_bound_smem + 3) & ~3);            // 16-byte aligned: read as float4 chunks
     __shared__ int2 s_queue[kWarps][kQueueCap];                  // (local row, bits of its h)
     __shared__ u64 s_keys[kWarps];
     __shared__ unsigned s_live[kWarps];
@@ -750,14 +762,24 @@ __global__ void __launch_bounds__(kThreads, CPL == 0 ? 2 : CS_MIN_BLOCKS) fps_st
         __syncwarp();
     };
 
-    auto load_tile = [&](const int t, float (&hq)[4], int (&vq)[4]) {
-        if (t >= tiles) return;
+    // h / voronoi of the next kScanDepth super-tiles of this warp travel through a warp-private ring
+    // of asynchronous 16-byte copies; a lane reads back exactly the bytes it copied itself, so the
+    // per-thread wait is the only synchronisation.  The ragged last super-tile is loaded directly.
+    auto issue_tile = [&](const int t, const int slot) {
+        if (vec_ok && t < whole_tiles) {
+            const int r0 = (t << 7) + 4 * lane;
+            cp_async16(&s_ring[warp][slot][4 * lane], s.h + r0);
+            if (!first) cp_async16(&s_ring[warp][slot][128 + 4 * lane], s.voronoi + r0);
+        }
+        cp_async_commit();                                       // one group per slot, empty or not
+    };
+    auto take_tile = [&](const int t, const int slot, float (&hq)[4], int (&vq)[4]) {
         const int r0 = (t << 7) + 4 * lane;
         if (vec_ok && t < whole_tiles) {
-            const float4 a = *reinterpret_cast<const float4*>(s.h + r0);
+            const float4 a = *reinterpret_cast<const float4*>(&s_ring[warp][slot][4 * lane]);
             hq[0] = a.x; hq[1] = a.y; hq[2] = a.z; hq[3] = a.w;
             if (!first) {
-                const int4 b = *reinterpret_cast<const int4*>(s.voronoi + r0);
+                const int4 b = *reinterpret_cast<const int4*>(&s_ring[warp][slot][128 + 4 * lane]);
                 vq[0] = b.x; vq[1] = b.y; vq[2] = b.z; vq[3] = b.w;
             }
         } else {
@@ -833,16 +855,21 @@ __global__ void __launch_bounds__(kThreads, CPL == 0 ? 2 : CS_MIN_BLOCKS) fps_st
         }
     };
 
-    // two register sets: the loads of the next super-tile are in flight while this one is scanned
-    float ha[4], hb[4];
-    int va[4] = {0, 0, 0, 0}, vb[4] = {0, 0, 0, 0};
-    int t = (int)blockIdx.x * kWarps + warp;
-    load_tile(t, ha, va);
-    for (; t < tiles; t += 2 * nw) {
-        load_tile(t + nw, hb, vb);
-        scan_tile(t, ha, va);
-        load_tile(t + 2 * nw, ha, va);
-        scan_tile(t + nw, hb, vb);
+    {
+        const int t0 = (int)blockIdx.x * kWarps + warp;
+#pragma unroll
+        for (int p = 0; p < kScanDepth; ++p) issue_tile(t0 + p * nw, p);
+        int n = 0;
+        for (int t = t0; t < tiles; t += nw, ++n) {
+            const int slot = n % kScanDepth;
+            cp_async_wait<kScanDepth - 1>();                     // the oldest group has landed
+            float hq[4];
+            int vq[4] = {0, 0, 0, 0};
+            take_tile(t, slot, hq, vq);
+            issue_tile(t + kScanDepth * nw, slot);               // refill the slot just read
+            scan_tile(t, hq, vq);
+        }
+        cp_async_wait<0>();
     }
     if (qn > 0) run_batch(0, qn);
 
@@ -1561,7 +1588,7 @@ int launch_step(const cs_state* s, unsigned mode, cudaStream_t st, int sms) {
     static thread_local size_t attr_set = 0, occ_smem = ~(size_t)0;
     static thread_local int occ_blocks = 0;
     const int n_bound = (int)(s->cap < kBoundSmemMax ? s->cap : kBoundSmemMax);
-    const size_t smem = (size_t)n_bound * sizeof(float) + (CPL ? 0 : (size_t)s->D * sizeof(float));
+    const size_t smem = ((size_t)((n_bound + 3) & ~3) + (CPL ? 0 : (size_t)s->D)) * sizeof(float);
     if (smem > 48 * 1024 && smem > attr_set) {
         if (cudaFuncSetAttribute(fps_step_kernel<CPL, FULL, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) {
@@ -1594,8 +1621,8 @@ int launch_step_queue(const cs_state* s, cudaStream_t st, int sms) {
     static thread_local size_t attr_set = 0, occ_smem = ~(size_t)0;
     static thread_local int occ_blocks = 0;
     const int n_bound = (int)(s->cap < kBoundSmemMax ? s->cap : kBoundSmemMax);
-    const size_t smem = (size_t)n_bound * sizeof(float) + (CPL ? 0 : (size_t)s->D * sizeof(float));
-    if (smem > 32 * 1024 && smem > attr_set) {
+    const size_t smem = ((size_t)kScanRingFloats + (size_t)((n_bound + 3) & ~3) + (CPL ? 0 : (size_t)s->D)) * sizeof(float);
+    if (smem > attr_set) {
         if (cudaFuncSetAttribute(fps_step_queue_kernel<CPL, FULL, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) {
             g_last_cuda = cudaGetLastError();

@@ -62,6 +62,7 @@ SHAPES = [
     (1500, 512, 64),
     (900, 1024, 48),    # eight chunks per lane
     (700, 1028, 40),    # D % 4 == 0 but wider than the register path: generic kernel
+    (300, 1032, 41),    # the same with a bound table whose length is not a multiple of four
     (1200, 100, 64),    # D % 4 == 0, 25 chunks
     (800, 50, 64),      # D % 4 != 0: the reference's scalar dot
     (600, 3, 40),
@@ -77,7 +78,8 @@ def test_fps_matches_oracle_prune(N, D, k):
 
 
 @pytest.mark.parametrize("N,D,k", [(33, 64, 20), (1000, 32, 128), (4097, 128, 300), (3000, 192, 64), (2500, 256, 200),
-                                   (900, 1024, 48), (1200, 100, 64), (20000, 36, 100), (130, 128, 130)])
+                                   (900, 1024, 48), (1200, 100, 64), (20000, 36, 100), (130, 128, 130),
+                                   (300, 1032, 41)])
 def test_fps_matches_oracle_prune_inline(N, D, k):
     """Prune mode with the rows evaluated where the scan meets them (no queue)."""
     from coresets_b200._native import MODE_PRUNE_INLINE
@@ -96,7 +98,7 @@ def test_fps_matches_oracle_prune_more_shapes(N, D, k):
 
 DENSE_SHAPES = [(33, 64, 20), (4097, 128, 300), (2500, 256, 100), (800, 50, 64), (900, 1024, 48), (3000, 192, 64),
                 (1200, 100, 64), (1000, 32, 128), (16383, 128, 256), (700, 1028, 40), (5, 128, 5), (20000, 36, 100),
-                (1500, 512, 64), (31, 8, 31), (1002, 64, 40), (258, 48, 30)]
+                (1500, 512, 64), (31, 8, 31), (1002, 64, 40), (258, 48, 30), (300, 1032, 41)]
 
 
 @pytest.mark.parametrize("N,D,k", DENSE_SHAPES)
