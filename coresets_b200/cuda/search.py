@@ -8,8 +8,8 @@ full budget.  Two strategies, both returning the same boundary for every monoton
   (src/coresets/cuda/multi/_base.py:735-747);
 * ``largest_true``   -- start at a seed (the previous layer's answer), walk in the direction the
   seed's verdict points to, stride 1 for the first ``linear`` successes and doubling afterwards,
-  then bisect the bracket (the reference's seeded walk, _base.py:751-809).  It never spends a
-  probe on m = 0, which cannot move the floor.
+  then bisect the bracket (the reference's seeded walk, _base.py:751-809).  A walk that starts at
+  seed 0 never spends a probe on m = 0, which cannot move the floor.
 """
 from __future__ import annotations
 
