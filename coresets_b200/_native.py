@@ -16,6 +16,7 @@ from . import build as _build
 CS_ABI_VERSION = 6
 SELECT_SCRATCH_BYTES = 8192
 F_ELEMENT_ORDER = 1
+F_TEST_STALL_PIPE = 0x100
 CS_CTL_BYTES = 256
 
 MODE_PRUNE = 0

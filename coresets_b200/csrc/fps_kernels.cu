@@ -915,7 +915,6 @@ constexpr RingCfg kRingNarrow{3, 1, 65536, 16};   // D <= 64
 constexpr RingCfg kRingMid{3, 1, 65536, 8};       // 64 < D <= 128
 constexpr RingCfg kRingWide{5, 1, 40960, 8};      // 128 < D <= 1024
 constexpr int kTmaMaxWarps = 16;
-constexpr int kSpinLimit = 1 << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* b, int count) {
@@ -927,14 +926,23 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* b) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity) {
-    for (int it = 0; it < kSpinLimit; ++it) {
-        uint32_t ok;
-        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                     : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
-        if (ok) return true;
+// Bounded wait on a phase of an mbarrier: gives up after limit_ns of wall time (checked every 64
+// polls) and returns false.
+__device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, unsigned long long limit_ns) {
+    if (mbar_try(b, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int it = 0; it < 64; ++it)
+            if (mbar_try(b, parity)) return true;
+        if (global_ns() - t0 > limit_ns) return false;
     }
-    return false;
 }
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* b) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -964,6 +972,9 @@ __global__ void __launch_bounds__((W + 1) * 32, B) fps_step_tma_kernel(const cs_
     const int n32 = (int)N;
     const int x_bytes = tile_rows * D * 4;
     const int stage_bytes = x_bytes + 3 * tile_rows * 4;
+    const unsigned long long pipe_limit_ns =
+        (unsigned long long)(s.xchg_timeout_ms > 0 ? s.xchg_timeout_ms : 10000) * 1000000ull;
+    const bool stall_for_test = (s.flags & CS_F_TEST_STALL_PIPE) != 0;   // the producer starts no copy
     const int ntiles = (int)((N + tile_rows - 1) / tile_rows);
     const int rpw = tile_rows / W;                           // rows of a tile per consumer warp (<= 32)
 
@@ -985,12 +996,12 @@ __global__ void __launch_bounds__((W + 1) * 32, B) fps_step_tma_kernel(const cs_
             int n = 0;
             for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++n, issued = n) {
                 const int q = n % S;
-                if (n >= S && !mbar_wait(&s_empty[q], (uint32_t)((n / S) - 1) & 1u)) {
+                if (n >= S && !mbar_wait(&s_empty[q], (uint32_t)((n / S) - 1) & 1u, pipe_limit_ns)) {
                     ctl->status = ST_PIPE_TIMEOUT;
                     s_abort = 1;
                     break;
                 }
-                if (*(volatile int*)&s_abort) break;
+                if (*(volatile int*)&s_abort || stall_for_test) break;
                 const int64_t row0 = (int64_t)t * tile_rows;
                 const int rows = (int)((N - row0) < tile_rows ? (N - row0) : tile_rows);
                 const int rows4 = rows & ~3;                       // a bulk copy moves multiples of 16 bytes
@@ -1027,7 +1038,7 @@ __global__ void __launch_bounds__((W + 1) * 32, B) fps_step_tma_kernel(const cs_
         int n = 0;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++n) {
             const int q = n % S;
-            if (!__all_sync(kFull, mbar_wait(&s_full[q], (uint32_t)(n / S) & 1u))) {   // warp-uniform verdict
+            if (!__all_sync(kFull, mbar_wait(&s_full[q], (uint32_t)(n / S) & 1u, pipe_limit_ns))) {   // warp-uniform verdict
                 if (lane == 0) { ctl->status = ST_PIPE_TIMEOUT; s_abort = 1; }
                 break;
             }
@@ -1132,7 +1143,8 @@ __global__ void __launch_bounds__((W + 1) * 32, B) fps_step_tma_kernel(const cs_
         // a wait ran out: let the copies that may still be in flight land before the block's
         // shared memory is released (each wait bounded): the last tile started on stage q was
         // number q + S * floor((issued - 1 - q) / S), whose phase parity is waited for
-        for (int q = 0; q < S && q < issued; ++q) (void)mbar_wait(&s_full[q], (uint32_t)((issued - 1 - q) / S) & 1u);
+        for (int q = 0; q < S && q < issued; ++q)
+            (void)mbar_wait(&s_full[q], (uint32_t)((issued - 1 - q) / S) & 1u, pipe_limit_ns);
     }
     const int slot = (i + 1) & 1;
     if (threadIdx.x == 0) {

@@ -119,6 +119,7 @@ class ShardEngine:
         self.group = group
         self.mode = default_mode() if mode is None else int(mode)
         self.element_order = bool(element_order)
+        self._extra_flags = 0            # test hooks of the C ABI (CS_F_TEST_*)
         dev = self.device
         f32, i32, i64 = torch.float32, torch.int32, torch.int64
         n_alloc = max(self.N_local, 1)
@@ -188,7 +189,7 @@ class ShardEngine:
         for r, ptr in enumerate(self.peer_ptrs):
             s.peer_win[r] = ptr
         s.xchg_timeout_ms = int(os.environ.get("CORESETS_B200_XCHG_TIMEOUT_MS", "10000"))
-        s.flags = _native.F_ELEMENT_ORDER if self.element_order else 0
+        s.flags = (_native.F_ELEMENT_ORDER if self.element_order else 0) | self._extra_flags
         return s
 
     def rebind(self, *, h: Optional[torch.Tensor] = None, voronoi: Optional[torch.Tensor] = None) -> None:
@@ -381,6 +382,7 @@ class ShardEngine:
         if view.status != 0:
             what = {1: "more picks were launched than the centre table can hold",
                     2: "a forced pick named a row this rank does not own",
-                    3: "timed out waiting for a peer's candidate (peer exchange)"}.get(view.status, "unknown")
+                    3: "timed out waiting for a peer's candidate (peer exchange)",
+                    4: "timed out waiting for a bulk copy (dense-mode pipe)"}.get(view.status, "unknown")
             raise RuntimeError(f"coresets_b200 device status {view.status}: {what}")
         return view

@@ -61,6 +61,8 @@ extern "C" {
                               ... with one fma each) even when D % 4 == 0: the order the reference uses
                               for float16 / float64 inputs (_shared.cuh:55-58), whose rows the caller
                               passes converted to float32 */
+#define CS_F_TEST_STALL_PIPE 0x100u /* test hook: the dense kernel's producer starts no copy, so that the
+                              consumers' bounded wait runs out (status 4) without any fault */
 /* cs_commit_bound flags */
 #define CS_RULE_NONE 0u    /* plain FPS: no separation bookkeeping */
 #define CS_RULE_SIM_SINGLE 1u   /* commit_center_with_sep_kernel rules (commit.cu:41-51) */
@@ -120,7 +122,8 @@ typedef struct cs_state {
     uint32_t* peer_win[CS_MAX_PEERS]; /* CS_XCHG_PEER: every rank's exchange window as mapped
                               into THIS process (peer_win[rank] is the local one); each holds
                               cs_xchg_window_words() zero-initialised 32-bit words             */
-    int32_t xchg_timeout_ms; /* bound of the flag wait (0 = 10 s); on expiry status becomes 3  */
+    int32_t xchg_timeout_ms; /* bound of every device-side wait (0 = 10 s): the exchange flag wait
+                              (status 3 on expiry) and the bulk-copy pipe of dense mode (status 4) */
     int32_t flags;         /* CS_F_* bits                                                     */
 } cs_state;
 

@@ -420,6 +420,33 @@ def test_peer_exchange_kernels_on_one_device(sizes, monkeypatch):
         np.testing.assert_array_equal(bits(e.h[:n].cpu().numpy()), bits(o_h[offs[r] : offs[r] + n]))
 
 
+def test_dense_pipe_wait_times_out_with_a_status(monkeypatch):
+    """The bulk-copy ring of dense mode with a producer that starts no copy (test hook): the
+    consumers' bounded mbarrier wait gives up, the status word says so, nothing faults and the
+    context stays usable."""
+    from coresets_b200._native import F_TEST_STALL_PIPE
+    monkeypatch.setenv("CORESETS_B200_XCHG_TIMEOUT_MS", "40")
+    dev = torch.device("cuda:0")
+    X = torch.from_numpy(gaussian_mixture(5000, 128, 4, seed=1)).to(dev)
+    eng = engine.ShardEngine(X, engine.row_norms(X), 8, mode=MODE_DENSE)
+    eng._extra_flags = F_TEST_STALL_PIPE
+    eng.state = eng._make_state()
+    eng.init_state()
+    eng.force_pick(0)
+    eng.commit()
+    eng.step()
+    with pytest.raises(RuntimeError, match="bulk copy"):
+        eng.check_status()
+    assert int(torch.ones(4, device="cuda").sum().item()) == 4
+    # the same engine without the hook works
+    eng._extra_flags = 0
+    eng.state = eng._make_state()
+    eng.init_state()
+    eng.pick_forced(0)
+    eng.run_picks(5)
+    assert eng.check_status().n_sel == 6
+
+
 def test_peer_exchange_wait_times_out_with_a_status(monkeypatch):
     """A peer that never publishes: the bounded wait gives up, the status word says so, the
     context stays usable."""
