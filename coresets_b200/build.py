@@ -17,8 +17,8 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
 LIB = Path(os.environ["CORESETS_B200_LIB"]) if os.environ.get("CORESETS_B200_LIB") else PKG / "libcoresets_b200.so"
-SOURCES = [PKG / "csrc" / "fps_kernels.cu"]
-HEADERS = [ROOT / "include" / "coresets_b200.h"]
+SOURCES = [PKG / "csrc" / "fps_kernels.cu"]          # one translation unit; the kernels live in csrc/*.cuh
+HEADERS = [ROOT / "include" / "coresets_b200.h", *sorted((PKG / "csrc").glob("*.cuh"))]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
