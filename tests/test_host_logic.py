@@ -79,3 +79,20 @@ def test_fps_cuda_float16_and_float64(fake_native, dtype, N, D, k):
 def test_fps_cuda_requires_cuda_tensor():
     with pytest.raises(ValueError, match="CUDA"):
         fps_mod.fps(torch.zeros(10, 4), 2)
+
+
+def test_resolve_max_k_budget_rule(monkeypatch):
+    """30 % of the free device bytes for two copies of the centre rows plus five scalars per
+    centre, capped by log2 N (src/coresets/cuda/multi/_shared.py:316-336, _internal/scratch.py:62-90)."""
+    from coresets_b200.cuda.accrete_core import resolve_max_k
+    dev = torch.device("cuda", 0)
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda device=None: (10 * 10**9, 180 * 10**9))
+    # budget 3e9 / (2*256*4 + 20) = 1 450 676 rows -> 2^20 fits, N = 1e6 caps at 19
+    assert resolve_max_k(None, 1_000_000, 256, 4, dev, strict=False, collective=False) == (19, 2 ** 19)
+    assert resolve_max_k(None, 10**9, 256, 4, dev, strict=False, collective=False) == (20, 2 ** 20)
+    assert resolve_max_k(7, 10**9, 256, 4, dev, strict=False, collective=False) == (7, 128)   # a pinned value is kept
+    assert resolve_max_k(20, 10**9, 256, 4, dev, strict=True, collective=False) == (20, 2 ** 20)
+    with pytest.raises(ValueError, match="Safe max_k for this GPU: 20"):
+        resolve_max_k(21, 10**9, 256, 4, dev, strict=True, collective=False)
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda device=None: (1000, 1000))
+    assert resolve_max_k(None, 10**6, 256, 4, dev, strict=False, collective=False) == (1, 2)  # never below one level
