@@ -62,7 +62,8 @@ def accrete_mode(cfg, rank, world) -> None:
     out = Path(cfg["out_dir"])
     try:
         for case in cfg["cases"]:
-            for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK", "CORESETS_LANES_MIN_STEPS"):
+            for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK", "CORESETS_LANES_MIN_STEPS", "CORESETS_BISECT_GALLOP_DEEP",
+                      "CORESETS_LAZY_FORWARD"):
                 os.environ.pop(k, None)
             os.environ.update(case.get("env", {}))
             X = np.load(case["x_path"])

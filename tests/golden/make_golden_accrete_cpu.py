@@ -7,7 +7,8 @@ The reference's `accrete` (src/coresets/cuda/accrete.py) and `accrete_voronoi_mu
 CUDA extension (tests/golden/ref_ext_cpu.py).  Writes tests/golden/accrete_cpu_<case>.npz with the
 returned index lists and the per-commit trace (phase, position, index, value, separation) of the
 single-GPU driver.  The sharded driver runs in a one-rank and a two-rank gloo group, with default
-knobs and with CORESETS_BISECT_SEED=1 CORESETS_FILL_CHUNK=256.
+knobs, with CORESETS_BISECT_SEED=1 CORESETS_FILL_CHUNK=256, with the deep gallop
+(CORESETS_BISECT_GALLOP_DEEP=1, CORESETS_FILL_CHUNK=64) and with CORESETS_LAZY_FORWARD=0.
 """
 from __future__ import annotations
 
@@ -76,7 +77,7 @@ def run_sharded(X, order, c, world, rank, knobs: dict):
     import torch.distributed as dist
     from coresets.cuda.multi.layout import compute_shard_layout
     from coresets.cuda.multi.sharded import accrete_voronoi_multi_sharded
-    for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK"):
+    for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK", "CORESETS_BISECT_GALLOP_DEEP", "CORESETS_LAZY_FORWARD"):
         os.environ.pop(k, None)
     os.environ.update(knobs)
     sizes, offs = compute_shard_layout(X.shape[0], world)
@@ -97,8 +98,11 @@ def worker(ref_root: str, out_dir: str):
         X, order = make_case(c)
         res = run_sharded(X, order, c, world, rank, {})
         res2 = run_sharded(X, order, c, world, rank, {"CORESETS_BISECT_SEED": "1", "CORESETS_FILL_CHUNK": "256"})
+        res3 = run_sharded(X, order, c, world, rank, {"CORESETS_BISECT_SEED": "1", "CORESETS_BISECT_GALLOP_DEEP": "1",
+                                                      "CORESETS_FILL_CHUNK": "64"})
+        res4 = run_sharded(X, order, c, world, rank, {"CORESETS_BISECT_SEED": "1", "CORESETS_LAZY_FORWARD": "0"})
         if rank == 0:
-            np.savez(Path(out_dir) / f"w{world}_{name}.npz", plain=res, knobs=res2)
+            np.savez(Path(out_dir) / f"w{world}_{name}.npz", plain=res, knobs=res2, deep=res3, nolazy=res4)
     dist.barrier()
     dist.destroy_process_group()
 
@@ -137,6 +141,8 @@ def main():
             z = np.load(Path(tmp) / f"w{world}_{name}.npz")
             rec[f"sharded_w{world}"] = z["plain"]
             rec[f"sharded_w{world}_knobs"] = z["knobs"]
+            rec[f"sharded_w{world}_deep"] = z["deep"]
+            rec[f"sharded_w{world}_nolazy"] = z["nolazy"]
         same = all(np.array_equal(rec["sharded_w1"], rec[k]) for k in rec if k.startswith("sharded_"))
         if "single" in rec:
             same = same and np.array_equal(rec["single"], rec["sharded_w1"])

@@ -62,6 +62,10 @@ def test_sharded_driver_matches_reference(tmp_path, world):
         # fused probe lanes forced on (they need long simulations by default): same list as without
         cases.append(dict(base, name=f"{name}_lanes", env={"CORESETS_BISECT_SEED": "1", "CORESETS_FILL_CHUNK": "256",
                                                           "CORESETS_LANES_MIN_STEPS": "4"}))
+        # knobs that change the probe schedule (and, on one case, the reference's list itself)
+        cases.append(dict(base, name=f"{name}_deep", env={"CORESETS_BISECT_SEED": "1", "CORESETS_BISECT_GALLOP_DEEP": "1",
+                                                         "CORESETS_FILL_CHUNK": "64"}))
+        cases.append(dict(base, name=f"{name}_nolazy", env={"CORESETS_BISECT_SEED": "1", "CORESETS_LAZY_FORWARD": "0"}))
     _run(world, dict(mode="accrete", cases=cases, out_dir=str(tmp_path)), timeout=900)
     for name in CASES:
         z = np.load(GOLDEN / f"accrete_cpu_{name}.npz")
@@ -69,6 +73,8 @@ def test_sharded_driver_matches_reference(tmp_path, world):
             np.testing.assert_array_equal(np.load(tmp_path / f"{name}_plain_{r}.npy"), z[f"sharded_w{world}"])
             np.testing.assert_array_equal(np.load(tmp_path / f"{name}_knobs_{r}.npy"), z[f"sharded_w{world}_knobs"])
             np.testing.assert_array_equal(np.load(tmp_path / f"{name}_lanes_{r}.npy"), z[f"sharded_w{world}_knobs"])
+            np.testing.assert_array_equal(np.load(tmp_path / f"{name}_deep_{r}.npy"), z[f"sharded_w{world}_deep"])
+            np.testing.assert_array_equal(np.load(tmp_path / f"{name}_nolazy_{r}.npy"), z[f"sharded_w{world}_nolazy"])
 
 
 def test_accrete_validation(fake_native):
