@@ -309,10 +309,18 @@ class AccreteDriver:
         if not self._key_valid:
             self.E.scan()
             self._key_valid = True
-        per_pick = self.trace.active
-        chunk = 1 if per_pick else (self.fill_chunk if self.fill_chunk > 0 else 256)
-        if self.checkpoint_every:
-            chunk = max(1, min(chunk, self.checkpoint_every))
+        # Safe points (where a mid-layer checkpoint may be written) follow the reference: after every
+        # chunk of CORESETS_FILL_CHUNK picks when that knob is set (sharded.py:219-295), after every
+        # pick otherwise (_base.py:528-540) -- there the picks still run in chunks, cut so that the
+        # checkpoint cadence falls on a chunk end.
+        if self.trace.active:
+            chunk = 1
+        elif self.fill_chunk > 0 and len(self.selected) > 0:
+            chunk = self.fill_chunk
+        else:
+            chunk = 256
+            if self.checkpoint_every:
+                chunk = max(1, min(chunk, self.checkpoint_every))
         while budget > 0:
             m = min(chunk, budget)
             n0 = len(self.selected)

@@ -83,3 +83,44 @@ def test_accrete_validation(fake_native):
         acc_mod.accrete(X[:0], X, torch.arange(0), 2, verbose=False)
     with pytest.raises(ValueError, match="mismatch"):
         acc_mod.accrete(X, torch.zeros(8, 5), torch.arange(8), 2, verbose=False)
+
+
+def test_checkpoint_files_match_the_reference_and_resume_reproduces_the_run(tmp_path):
+    """Layer checkpoints of the sharded driver (`<prefix>_kKK.npy`, `_kKK_sep.npy`, `_latest.txt`,
+    `_seeds.npy`; src/coresets/cuda/multi/sharded.py:493-549, 754-775) against the files the
+    reference wrote for the same run (tests/golden/make_golden_accrete_ckpt.py), then a resume
+    from the last but one layer.  This package resumes by replaying the stored picks through the
+    same kernels, so the resumed list equals the uninterrupted one; the reference rebuilds its
+    state with a matrix product and its own resumed list differs from its own full run on this
+    case (kept in the fixture as `resumed`)."""
+    from tests.golden.make_golden_accrete_ckpt import CASE, EVERY, KNOBS
+    z = np.load(GOLDEN / "accrete_cpu_ckpt.npz")
+    c = CASES[CASE]
+    X, order = make_case(c)
+    np.save(tmp_path / "x.npy", X)
+    np.save(tmp_path / "o.npy", order)
+    base = dict(x_path=str(tmp_path / "x.npy"), order_path=str(tmp_path / "o.npy"), n_anchor=c["n_anchor"],
+                max_k=c["max_k"], env=KNOBS)
+    _run(1, dict(mode="accrete", out_dir=str(tmp_path),
+                 cases=[dict(base, name="full", checkpoint="ck", checkpoint_every=EVERY)]), timeout=600)
+    full = np.load(tmp_path / "full_0.npy")
+    np.testing.assert_array_equal(full, z["full"])
+    names = sorted(p.name for p in tmp_path.iterdir() if p.name.startswith("ck_"))
+    assert names == [str(n) for n in z["names"]]
+    for n in names:
+        want = z["file:" + n]
+        if n.endswith(".npy"):
+            got = np.load(tmp_path / n)
+            assert got.dtype == want.dtype and got.shape == want.shape, n
+            np.testing.assert_array_equal(got.view(np.int64) if got.dtype == np.float64 else got,
+                                          want.view(np.int64) if want.dtype == np.float64 else want, err_msg=n)
+        else:
+            assert (tmp_path / n).read_text() == str(want), n
+    top = c["max_k"]
+    for n in names:
+        if f"_k{top:02d}" in n:
+            (tmp_path / n).unlink()
+    (tmp_path / "ck_latest.txt").write_text(f"{top - 1}\n")
+    _run(1, dict(mode="accrete", out_dir=str(tmp_path), cases=[dict(base, name="again", resume="ck")]), timeout=600)
+    np.testing.assert_array_equal(np.load(tmp_path / "again_0.npy"), full)
+    assert not np.array_equal(z["resumed"], z["full"])      # the reference's own resume is not reproducible here
