@@ -552,8 +552,9 @@ class AccreteDriver:
         cov_sq = max(0.0, self._global_max(self.E.h))
         sep_val, cov_val, rel_gap = invariant_numbers(cov_sq, sep_sq)
         if math.isfinite(sep_sq) and sep_sq < cov_sq * relax * relax * (1.0 - _GROSS_REL):
+            where = f"k={k}" if self.multi else f"level k={k}"        # the two flavours' wording (_shared.py:365, diag.py:103)
             raise RuntimeError(
-                f"{self.name}: sep > cov violated at k={k} (size={target_size}): sep={sep_val:.8e}, "
+                f"{self.name}: sep > cov violated at {where} (size={target_size}): sep={sep_val:.8e}, "
                 f"cov={cov_val:.8e}, rel_gap={rel_gap:.3e}. Gross violation, not float noise."
             )
         return sep_val, cov_val, rel_gap
