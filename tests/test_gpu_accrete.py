@@ -59,3 +59,20 @@ def test_accrete_sharded_peer_exchange_matches_reference(tmp_path, world):
         pytest.skip(f"needs {world} GPUs")
     _launch(world, dict(mode="accrete", cases=[], out_dir=str(tmp_path)), timeout=1500,
             extra_env={"CORESETS_B200_EXCHANGE": "p2p", "CORESETS_B200_XCHG_TIMEOUT_MS": "5000"})
+
+
+def test_float16_gross_violation_is_reported_like_the_reference():
+    """On the clustered-jitter matrix in float16 the reference's own invariant check aborts
+    (`accrete`, 6000 x 64, 3000 anchors, max_k = 9, run on a B200): "sep > cov violated at level
+    k=9 (size=512): sep=5.66210904e-01, cov=5.69710191e-01, rel_gap=-1.225e-02".  The same input
+    must fail here at the same layer with the same numbers (they depend on every bit of h)."""
+    import coresets_b200
+    from tests.data import as_dtype, clustered_jitter
+    X = torch.from_numpy(as_dtype(clustered_jitter(6000, 64, seed=42), "float16")).cuda()
+    order = torch.arange(3000, dtype=torch.long, device="cuda")
+    with pytest.raises(RuntimeError) as ei:
+        coresets_b200.accrete(X[:3000], X[3000:], order, 9, verbose=False)
+    msg = str(ei.value)
+    assert "accrete: sep > cov violated at level k=9 (size=512)" in msg
+    assert "sep=5.66210904e-01, cov=5.69710191e-01, rel_gap=-1.225e-02" in msg
+    assert msg.endswith("Gross violation, not float noise.")
