@@ -5,7 +5,8 @@
 Runs `accrete` (src/coresets/cuda/accrete.py) and the one-rank `accrete_voronoi_multi_sharded`
 (src/coresets/cuda/multi/sharded.py) on CPU tensors with the oracle as kernel extension and keeps
 what they print, with every wall-clock figure replaced by `T` (see `mask`).  Writes
-tests/golden/verbose_single.txt and tests/golden/verbose_sharded.txt.
+tests/golden/verbose_single.txt, verbose_sharded.txt and verbose_sharded_knobs.txt (the seeded
+walk: CORESETS_BISECT_SEED=1 CORESETS_FILL_CHUNK=256 on a second case).
 """
 from __future__ import annotations
 
@@ -25,6 +26,8 @@ sys.path.insert(0, str(ROOT))
 from tests.golden.make_golden_accrete_cpu import CASES, make_case, setup_reference  # noqa: E402
 
 CASE = "jitter_1024x8_k128"
+CASE_KNOBS = "mix_3000x16_k256_fps"
+KNOBS = {"CORESETS_BISECT_SEED": "1", "CORESETS_FILL_CHUNK": "256"}
 
 
 def mask(text: str) -> str:
@@ -71,6 +74,15 @@ def main() -> None:
         accrete_voronoi_multi_sharded(Xt, 0, 1, c["n_anchor"], X.shape[0], [X.shape[0]], torch.from_numpy(order),
                                       max_k=c["max_k"], verbose=True, profile=True)
     (Path(__file__).parent / "verbose_sharded.txt").write_text(mask(buf.getvalue()))
+    # the seeded walk with lazy forward and chunked fill on a second case
+    c2 = CASES[CASE_KNOBS]
+    X2, order2 = make_case(c2)
+    os.environ.update(KNOBS)
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        accrete_voronoi_multi_sharded(torch.from_numpy(X2), 0, 1, c2["n_anchor"], X2.shape[0], [X2.shape[0]],
+                                      torch.from_numpy(order2), max_k=c2["max_k"], verbose=True, profile=False)
+    (Path(__file__).parent / "verbose_sharded_knobs.txt").write_text(mask(buf.getvalue()))
     dist.destroy_process_group()
     print(mask(buf.getvalue()))
 

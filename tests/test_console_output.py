@@ -12,16 +12,18 @@ import torch
 from coresets_b200 import _native
 from tests.fake_native import FakeNative
 from tests.golden.make_golden_accrete_cpu import CASES, make_case
-from tests.golden.make_golden_verbose import CASE, mask
+from tests.golden.make_golden_verbose import CASE, CASE_KNOBS, KNOBS, mask
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
-def _setup(monkeypatch):
+def _setup(monkeypatch, case=CASE, knobs=None):
     monkeypatch.setattr(_native, "_native", FakeNative())
     for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK", "CORESETS_LAZY_FORWARD", "CORESETS_BISECT_GALLOP_DEEP"):
         monkeypatch.delenv(k, raising=False)
-    c = CASES[CASE]
+    for k, v in (knobs or {}).items():
+        monkeypatch.setenv(k, v)
+    c = CASES[case]
     X, order = make_case(c)
     return c, torch.from_numpy(X), torch.from_numpy(order)
 
@@ -36,13 +38,17 @@ def test_single_driver_console_output(monkeypatch):
     assert mask(buf.getvalue()) == (GOLDEN / "verbose_single.txt").read_text()
 
 
-def test_sharded_driver_console_output(monkeypatch):
-    import os
+import pytest
+
+
+@pytest.mark.parametrize("case,knobs,golden,profile", [(CASE, None, "verbose_sharded.txt", True),
+                                                       (CASE_KNOBS, KNOBS, "verbose_sharded_knobs.txt", False)])
+def test_sharded_driver_console_output(monkeypatch, case, knobs, golden, profile):
     import socket
     import torch.distributed as dist
     sh = importlib.import_module("coresets_b200.cuda.multi.sharded")
     monkeypatch.setattr(sh, "_REQUIRE_CUDA", False)
-    c, X, order = _setup(monkeypatch)
+    c, X, order = _setup(monkeypatch, case, knobs)
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
@@ -53,8 +59,8 @@ def test_sharded_driver_console_output(monkeypatch):
         buf = io.StringIO()
         with contextlib.redirect_stdout(buf):
             sh.accrete_voronoi_multi_sharded(X, 0, 1, c["n_anchor"], X.shape[0], [X.shape[0]], order,
-                                             max_k=c["max_k"], verbose=True, profile=True)
+                                             max_k=c["max_k"], verbose=True, profile=profile)
     finally:
         dist.destroy_process_group()
-    got, want = mask(buf.getvalue()), (GOLDEN / "verbose_sharded.txt").read_text()
+    got, want = mask(buf.getvalue()), (GOLDEN / golden).read_text()
     assert got.splitlines() == want.splitlines()
