@@ -75,6 +75,8 @@ def accrete_mode(cfg, rank, world) -> None:
                 kw.update(checkpoint_path=str(out / case["checkpoint"]), checkpoint_every=case.get("checkpoint_every", 0))
             if case.get("resume"):
                 kw.update(resume_from=str(out / case["resume"]))
+            if case.get("trace"):
+                kw.update(trace_path=str(out / f"{case['name']}_trace_{rank}.tsv"))
             res = sh.accrete_voronoi_multi_sharded(
                 Xl, rank, world, case["n_anchor"], X.shape[0], sizes, torch.from_numpy(order),
                 max_k=case["max_k"], n_target=case.get("n_target"), verbose=False, **kw)

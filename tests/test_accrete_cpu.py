@@ -124,3 +124,30 @@ def test_checkpoint_files_match_the_reference_and_resume_reproduces_the_run(tmp_
     _run(1, dict(mode="accrete", out_dir=str(tmp_path), cases=[dict(base, name="again", resume="ck")]), timeout=600)
     np.testing.assert_array_equal(np.load(tmp_path / "again_0.npy"), full)
     assert not np.array_equal(z["resumed"], z["full"])      # the reference's own resume is not reproducible here
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_sharded_driver_trace_matches_the_reference(tmp_path, world):
+    """Per-commit trace of the sharded driver (forward / replay / fill lines with value and
+    running separation, bit for bit) against the reference's own one-rank trace; the trace does not
+    depend on the number of ranks."""
+    from tests.golden.make_golden_accrete_traces import KNOB_SETS, TRACE_CASES
+    z = np.load(GOLDEN / "accrete_cpu_sharded_traces.npz")
+    cases = []
+    for name in TRACE_CASES:
+        c = CASES[name]
+        X, order = make_case(c)
+        np.save(tmp_path / f"{name}_x.npy", X)
+        np.save(tmp_path / f"{name}_o.npy", order)
+        for tag, env in KNOB_SETS.items():
+            cases.append(dict(x_path=str(tmp_path / f"{name}_x.npy"), order_path=str(tmp_path / f"{name}_o.npy"),
+                              n_anchor=c["n_anchor"], max_k=c["max_k"], name=f"{name}_{tag}", env=env, trace=True))
+    _run(world, dict(mode="accrete", cases=cases, out_dir=str(tmp_path)), timeout=900)
+    for name in TRACE_CASES:
+        for tag in KNOB_SETS:
+            mine = read_trace(str(tmp_path / f"{name}_{tag}_trace_0.tsv"))
+            for key in ("trace_phase", "trace_pos", "trace_idx"):
+                np.testing.assert_array_equal(mine[key], z[f"{name}:{tag}:{key}"], err_msg=f"{name} {tag} {key}")
+            for key in ("trace_val", "trace_sep"):
+                np.testing.assert_array_equal(mine[key].view(np.int64), z[f"{name}:{tag}:{key}"].view(np.int64),
+                                              err_msg=f"{name} {tag} {key}")
