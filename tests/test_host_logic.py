@@ -96,3 +96,23 @@ def test_resolve_max_k_budget_rule(monkeypatch):
         resolve_max_k(21, 10**9, 256, 4, dev, strict=True, collective=False)
     monkeypatch.setattr(torch.cuda, "mem_get_info", lambda device=None: (1000, 1000))
     assert resolve_max_k(None, 10**6, 256, 4, dev, strict=False, collective=False) == (1, 2)  # never below one level
+
+
+def test_torch_backend_fps_reproduces_the_reference_python_fps():
+    """``coresets_b200.fps`` (plain torch) against the outputs of the reference's own ``coresets.fps``
+    (tests/golden/cpu_fps_c1.npz, written by tests/golden/make_golden_cpu.py)."""
+    from pathlib import Path
+    import numpy as np
+    import torch
+    import coresets_b200
+    from tests.data import gaussian_mixture
+    z = np.load(Path(__file__).resolve().parent / "golden" / "cpu_fps_c1.npz")
+    X = torch.from_numpy(gaussian_mixture(20000, 64, 16, seed=0))
+    torch.set_num_threads(1)
+    sel, eps, h, v = coresets_b200.fps(X, 512)
+    np.testing.assert_array_equal(sel.numpy(), z["selected"])
+    np.testing.assert_allclose(eps.numpy(), z["eps"], rtol=1e-6)
+    np.testing.assert_array_equal(v.numpy().astype(np.int16), z["voronoi"])
+    assert eps[0] == 0.0 and "fps" in coresets_b200.__all__
+    seeded = coresets_b200.fps(X[:500], 5, torch.tensor([7, 3]))
+    assert seeded[0][:2].tolist() == [7, 3] and float(seeded[1][0]) == 0.0 and float(seeded[1][1]) > 0.0
