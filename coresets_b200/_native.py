@@ -13,11 +13,13 @@ from typing import Optional
 
 from . import build as _build
 
-CS_ABI_VERSION = 6
+CS_ABI_VERSION = 7
 SELECT_SCRATCH_BYTES = 8192
 F_ELEMENT_ORDER = 1
 F_TEST_STALL_PIPE = 0x100
 CS_CTL_BYTES = 256
+CELL_TILE = 256
+CELLS_META_BYTES = 128
 
 MODE_PRUNE = 0
 MODE_DENSE = 1
@@ -34,7 +36,7 @@ EXPORTS = (
     "cs_version", "cs_error_string", "cs_last_cuda_error", "cs_device_check", "cs_init_state",
     "cs_reset_ctl", "cs_force_pick", "cs_commit_bound", "cs_fps_step", "cs_sim_begin",
     "cs_sim_final_check", "cs_xchg_window_words", "cs_xchg_wait", "cs_scan_argmax", "cs_fps_step_lanes", "cs_fps_step_noalloc",
-    "cs_select_kth_largest", "cs_pool_argmax",
+    "cs_select_kth_largest", "cs_pool_argmax", "cs_cells_build", "cs_cells_select", "cs_fps_step_cells",
 )
 
 
@@ -64,6 +66,46 @@ class CsState(ctypes.Structure):
         ("xchg_timeout_ms", ctypes.c_int32),
         ("flags", ctypes.c_int32),
     ]
+
+
+class CsCells(ctypes.Structure):
+    """``cs_cells`` of include/coresets_b200.h."""
+    _fields_ = [
+        ("perm", ctypes.c_void_p),
+        ("hp", ctypes.c_void_p),
+        ("vp", ctypes.c_void_p),
+        ("cell0", ctypes.c_void_p),
+        ("slots", ctypes.c_int64),
+        ("seg_start", ctypes.c_void_p),
+        ("seg_count", ctypes.c_void_p),
+        ("seg_key", ctypes.c_void_p),
+        ("seg_h0", ctypes.c_void_p),
+        ("cursor", ctypes.c_void_p),
+        ("work_cell", ctypes.c_void_p),
+        ("work_cum", ctypes.c_void_p),
+        ("meta", ctypes.c_void_p),
+        ("queue", ctypes.c_void_p),
+        ("row_norm_max", ctypes.c_float),
+        ("q_cap", ctypes.c_int32),
+    ]
+
+
+class CellsMetaView(ctypes.Structure):
+    """``cs_cells_meta_view`` of include/coresets_b200.h."""
+    _fields_ = [
+        ("n_cells", ctypes.c_int32),
+        ("n_work", ctypes.c_int32),
+        ("n_chunks", ctypes.c_int32),
+        ("total_slots", ctypes.c_int32),
+        ("visited_slots", ctypes.c_uint64),
+        ("picks", ctypes.c_uint64),
+        ("q_count", ctypes.c_uint32),
+        ("q_inline", ctypes.c_uint32),
+        ("reserved", ctypes.c_uint8 * (CELLS_META_BYTES - 40)),
+    ]
+
+
+assert ctypes.sizeof(CellsMetaView) == CELLS_META_BYTES
 
 
 def decode_key(key: int):
@@ -144,6 +186,9 @@ class Native:
             ("cs_pool_argmax", [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, vp, vp]),
             ("cs_xchg_wait", [sp, vp]),
             ("cs_fps_step_lanes", [sp, ctypes.c_int32, ctypes.c_uint32, vp]),
+            ("cs_cells_build", [sp, ctypes.POINTER(CsCells), vp]),
+            ("cs_cells_select", [sp, ctypes.POINTER(CsCells), vp]),
+            ("cs_fps_step_cells", [sp, ctypes.POINTER(CsCells), vp]),
         ):
             fn = getattr(L, name)
             fn.restype = ctypes.c_int
@@ -217,6 +262,15 @@ class Native:
         self._check(self.lib.cs_fps_step_noalloc(X, norms, h, voronoi, N_local, D, shard_offset, centre,
                                                  norm_new, dSL, sel_pos, mode, out_key, out_live_rows, stream),
                     "cs_fps_step_noalloc")
+
+    def cells_build(self, s: CsState, c: CsCells, stream: int) -> None:
+        self._check(self.lib.cs_cells_build(ctypes.byref(s), ctypes.byref(c), stream), "cs_cells_build")
+
+    def cells_select(self, s: CsState, c: CsCells, stream: int) -> None:
+        self._check(self.lib.cs_cells_select(ctypes.byref(s), ctypes.byref(c), stream), "cs_cells_select")
+
+    def fps_step_cells(self, s: CsState, c: CsCells, stream: int) -> None:
+        self._check(self.lib.cs_fps_step_cells(ctypes.byref(s), ctypes.byref(c), stream), "cs_fps_step_cells")
 
     def fps_step_lanes(self, lanes, n_lanes: int, mode: int, stream: int) -> None:
         self._check(self.lib.cs_fps_step_lanes(lanes, n_lanes, mode, stream), "cs_fps_step_lanes")

@@ -16,6 +16,7 @@
 //   step_lanes.cuh     several states sharing one pass over X
 //   small_kernels.cuh  state set-up kernels, stand-alone arg-max scan
 //   select.cuh         exact k-th largest, arg-max over a list of rows
+//   cells.cuh          cell index: rows grouped by centre, picks that read only the cells that can change
 //
 // Arithmetic is spelled with __fmul_rn/__fmaf_rn/__fadd_rn so that no compiler contraction or
 // reassociation can change a bit; the file is compiled with -ftz=true because the reference
@@ -35,15 +36,18 @@
 #include "step_lanes.cuh"
 #include "small_kernels.cuh"
 #include "select.cuh"
+#include "cells.cuh"
 
 namespace {
 
 // ---- host side ---------------------------------------------------------------------------------
 struct DevInfo {
+    int dev = 0;
     int sms = 0;
     int cc_major = 0;
     bool ok = false;
 };
+constexpr int kMaxDevices = 64;
 DevInfo device_info() {
     static thread_local int cached_dev = -1;
     static thread_local DevInfo info;
@@ -51,6 +55,8 @@ DevInfo device_info() {
     if (cudaGetDevice(&dev) != cudaSuccess) return DevInfo();
     if (dev != cached_dev) {
         DevInfo d;
+        d.dev = dev;
+        if (dev < 0 || dev >= kMaxDevices) return DevInfo();
         if (cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return DevInfo();
         if (cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return DevInfo();
         d.ok = true;
@@ -65,6 +71,39 @@ int check_launch() {
     if (e != cudaSuccess) {
         g_last_cuda = e;
         return CS_E_LAUNCH;
+    }
+    return CS_OK;
+}
+
+// Per kernel, per device: the dynamic shared-memory size opted into and the resident blocks per SM
+// found for the last shared-memory size.  cudaFuncSetAttribute applies to the device that is
+// current, so a thread that moves to another device must opt in there again.
+struct KernelTune {
+    size_t attr_set[kMaxDevices];
+    size_t occ_smem[kMaxDevices];
+    int occ_blocks[kMaxDevices];
+};
+template <typename K>
+int tune_kernel(K kernel, KernelTune& t, const int dev, const size_t smem, const int threads, int* blocks_per_sm) {
+    // (opt in whenever the dynamic part grows: with the kernel's static part the total may pass 48 KB sooner)
+    if (smem > t.attr_set[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            g_last_cuda = cudaGetLastError();
+            return CS_E_LAUNCH;
+        }
+        t.attr_set[dev] = smem;
+    }
+    if (blocks_per_sm) {
+        if (t.occ_blocks[dev] == 0 || t.occ_smem[dev] != smem) {
+            int per_sm = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess || per_sm < 1) {
+                g_last_cuda = cudaGetLastError();
+                return CS_E_LAUNCH;
+            }
+            t.occ_blocks[dev] = per_sm;
+            t.occ_smem[dev] = smem;
+        }
+        *blocks_per_sm = t.occ_blocks[dev];
     }
     return CS_OK;
 }
@@ -91,7 +130,8 @@ int validate(const cs_state* s) {
 }
 
 template <int CPL, bool HALF, int S, int B, int T, int W>
-int launch_step_tma(const cs_state* s, cudaStream_t st, int sms) {
+int launch_step_tma(const cs_state* s, cudaStream_t st, const DevInfo& dv) {
+    const int sms = dv.sms;
     static_assert(W <= kTmaMaxWarps && (W % 8) == 0, "consumer warps");
     const int D = s->D;
     int tile_rows = T / (D * 4);
@@ -99,15 +139,9 @@ int launch_step_tma(const cs_state* s, cudaStream_t st, int sms) {
     tile_rows -= tile_rows % W;                             // W is a multiple of 8: 16-byte multiples of h / voronoi / norms
     if (tile_rows < W) tile_rows = W;
     const size_t smem = (size_t)S * tile_rows * (D * 4 + 12);   // rows of X, then h / voronoi / norm words
-    static thread_local size_t attr_set = 0;
-    if (smem > attr_set) {
-        if (cudaFuncSetAttribute(fps_step_tma_kernel<CPL, S, HALF, W, B>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem) != cudaSuccess) {
-            g_last_cuda = cudaGetLastError();
-            return CS_E_LAUNCH;
-        }
-        attr_set = smem;
-    }
+    static thread_local KernelTune tune;
+    const int rc = tune_kernel(fps_step_tma_kernel<CPL, S, HALF, W, B>, tune, dv.dev, smem, (W + 1) * 32, nullptr);
+    if (rc) return rc;
     const int64_t ntiles = (s->N_local + tile_rows - 1) / tile_rows;
     int64_t cap = (int64_t)sms * B;                         // resident blocks, each with its own ring
     int grid = (int)(ntiles < 1 ? 1 : (ntiles < cap ? ntiles : cap));
@@ -118,29 +152,14 @@ int launch_step_tma(const cs_state* s, cudaStream_t st, int sms) {
 constexpr int kBoundSmemMax = 16384;     // triangle bounds staged in shared memory (64 KB)
 
 template <int CPL, bool FULL, bool HALF = false>
-int launch_step(const cs_state* s, unsigned mode, cudaStream_t st, int sms) {
-    static thread_local size_t attr_set = 0, occ_smem = ~(size_t)0;
-    static thread_local int occ_blocks = 0;
+int launch_step(const cs_state* s, unsigned mode, cudaStream_t st, const DevInfo& dv) {
+    const int sms = dv.sms;
+    static thread_local KernelTune tune;
+    int occ_blocks = 0;
     const int n_bound = (int)(s->cap < kBoundSmemMax ? s->cap : kBoundSmemMax);
     const size_t smem = ((size_t)((n_bound + 3) & ~3) + (CPL ? 0 : (size_t)s->D)) * sizeof(float);
-    if (smem > 48 * 1024 && smem > attr_set) {
-        if (cudaFuncSetAttribute(fps_step_kernel<CPL, FULL, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem) != cudaSuccess) {
-            g_last_cuda = cudaGetLastError();
-            return CS_E_LAUNCH;
-        }
-        attr_set = smem;
-    }
-    if (occ_smem != smem) {
-        int per_sm = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fps_step_kernel<CPL, FULL, HALF>, kThreads, smem) !=
-                cudaSuccess || per_sm < 1) {
-            g_last_cuda = cudaGetLastError();
-            return CS_E_LAUNCH;
-        }
-        occ_blocks = per_sm;
-        occ_smem = smem;
-    }
+    const int rc = tune_kernel(fps_step_kernel<CPL, FULL, HALF>, tune, dv.dev, smem, kThreads, &occ_blocks);
+    if (rc) return rc;
     const int64_t tiles = (s->N_local + (32 * kRowsPerLane - 1)) >> kTileShift;
     int64_t want = (tiles + kWarps - 1) / kWarps;
     int64_t cap = (int64_t)sms * occ_blocks;     // persistent grid: a multiple of the SM count
@@ -151,29 +170,14 @@ int launch_step(const cs_state* s, unsigned mode, cudaStream_t st, int sms) {
 
 // prune mode with deferred rows (rows in whole 16-byte chunks, D <= 1024)
 template <int CPL, bool FULL, bool HALF = false>
-int launch_step_queue(const cs_state* s, cudaStream_t st, int sms) {
-    static thread_local size_t attr_set = 0, occ_smem = ~(size_t)0;
-    static thread_local int occ_blocks = 0;
+int launch_step_queue(const cs_state* s, cudaStream_t st, const DevInfo& dv) {
+    const int sms = dv.sms;
+    static thread_local KernelTune tune;
+    int occ_blocks = 0;
     const int n_bound = (int)(s->cap < kBoundSmemMax ? s->cap : kBoundSmemMax);
     const size_t smem = ((size_t)kScanRingFloats + (size_t)((n_bound + 3) & ~3) + (CPL ? 0 : (size_t)s->D)) * sizeof(float);
-    if (smem > attr_set) {
-        if (cudaFuncSetAttribute(fps_step_queue_kernel<CPL, FULL, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem) != cudaSuccess) {
-            g_last_cuda = cudaGetLastError();
-            return CS_E_LAUNCH;
-        }
-        attr_set = smem;
-    }
-    if (occ_smem != smem) {
-        int per_sm = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fps_step_queue_kernel<CPL, FULL, HALF>, kThreads,
-                                                          smem) != cudaSuccess || per_sm < 1) {
-            g_last_cuda = cudaGetLastError();
-            return CS_E_LAUNCH;
-        }
-        occ_blocks = per_sm;
-        occ_smem = smem;
-    }
+    const int rc = tune_kernel(fps_step_queue_kernel<CPL, FULL, HALF>, tune, dv.dev, smem, kThreads, &occ_blocks);
+    if (rc) return rc;
     const int64_t tiles = (s->N_local + 127) >> 7;
     int64_t want = (tiles + kWarps - 1) / kWarps;
     int64_t cap = (int64_t)sms * occ_blocks;     // persistent grid: a multiple of the SM count
@@ -183,17 +187,13 @@ int launch_step_queue(const cs_state* s, cudaStream_t st, int sms) {
 }
 
 template <int L, int CPL>
-int launch_lanes_t(const LaneSet& ls, unsigned mode, cudaStream_t st, int sms) {
+int launch_lanes_t(const LaneSet& ls, unsigned mode, cudaStream_t st, const DevInfo& dv) {
+    const int sms = dv.sms;
     const size_t smem = (size_t)L * ls.s[0].D * sizeof(float);
-    static thread_local int per_sm = 0;
-    if (per_sm == 0) {
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fps_step_lanes_kernel<L, CPL>, kThreads, smem) !=
-                cudaSuccess || per_sm < 1) {
-            g_last_cuda = cudaGetLastError();
-            per_sm = 0;
-            return CS_E_LAUNCH;
-        }
-    }
+    static thread_local KernelTune tune;
+    int per_sm = 0;
+    const int rc = tune_kernel(fps_step_lanes_kernel<L, CPL>, tune, dv.dev, smem, kThreads, &per_sm);
+    if (rc) return rc;
     const int64_t tiles = (ls.s[0].N_local + 31) >> 5;
     int64_t want = (tiles + kWarps - 1) / kWarps;
     int64_t cap = (int64_t)sms * per_sm;
@@ -203,7 +203,7 @@ int launch_lanes_t(const LaneSet& ls, unsigned mode, cudaStream_t st, int sms) {
 }
 
 template <int L>
-int launch_lanes_l(const LaneSet& ls, unsigned mode, cudaStream_t st, int sms) {
+int launch_lanes_l(const LaneSet& ls, unsigned mode, cudaStream_t st, const DevInfo& sms) {
     const int D = ls.s[0].D;
     if (D <= 128) return launch_lanes_t<L, 1>(ls, mode, st, sms);
     if (D <= 256) return launch_lanes_t<L, 2>(ls, mode, st, sms);
@@ -211,7 +211,7 @@ int launch_lanes_l(const LaneSet& ls, unsigned mode, cudaStream_t st, int sms) {
     return launch_lanes_t<L, 8>(ls, mode, st, sms);
 }
 
-int launch_lanes(const LaneSet& ls, int n, unsigned mode, cudaStream_t st, int sms) {
+int launch_lanes(const LaneSet& ls, int n, unsigned mode, cudaStream_t st, const DevInfo& sms) {
     switch (n) {
         case 2: return launch_lanes_l<2>(ls, mode, st, sms);
         case 3: return launch_lanes_l<3>(ls, mode, st, sms);
@@ -315,41 +315,41 @@ int cs_fps_step(const cs_state* s, uint32_t mode, cs_stream stream) {
     const bool bulk_ok = (((uintptr_t)s->X | (uintptr_t)s->h | (uintptr_t)s->voronoi | (uintptr_t)s->norms) & 15u) == 0;
     const bool element_order = (s->flags & CS_F_ELEMENT_ORDER) != 0;
     if (mode == CS_MODE_DENSE && bulk_ok && !element_order && (D & 3) == 0 && D >= 32 && D <= 1024 && s->N_local > 0) {
-        if (D <= 64) return launch_step_tma<1, true, kRingNarrow.stages, kRingNarrow.blocks, kRingNarrow.tile_bytes, kRingNarrow.warps>(s, st, d.sms);
-        if (D <= 128) return launch_step_tma<1, false, kRingMid.stages, kRingMid.blocks, kRingMid.tile_bytes, kRingMid.warps>(s, st, d.sms);
-        if (D <= 256) return launch_step_tma<2, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d.sms);
-        if (D <= 512) return launch_step_tma<4, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d.sms);
-        return launch_step_tma<8, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d.sms);
+        if (D <= 64) return launch_step_tma<1, true, kRingNarrow.stages, kRingNarrow.blocks, kRingNarrow.tile_bytes, kRingNarrow.warps>(s, st, d);
+        if (D <= 128) return launch_step_tma<1, false, kRingMid.stages, kRingMid.blocks, kRingMid.tile_bytes, kRingMid.warps>(s, st, d);
+        if (D <= 256) return launch_step_tma<2, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d);
+        if (D <= 512) return launch_step_tma<4, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d);
+        return launch_step_tma<8, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d);
     }
     const bool generic = element_order || (D & 3) != 0 || D > 1024;
-    if (generic && mode == CS_MODE_PRUNE && s->N_local > 0 && D <= 16384) return launch_step_queue<0, false>(s, st, d.sms);
-    if (generic) return launch_step<0, false>(s, mode, st, d.sms);
+    if (generic && mode == CS_MODE_PRUNE && s->N_local > 0 && D <= 16384) return launch_step_queue<0, false>(s, st, d);
+    if (generic) return launch_step<0, false>(s, mode, st, d);
     if (mode == CS_MODE_PRUNE && s->N_local > 0) {
         switch (D) {
-            case 128: return launch_step_queue<1, true>(s, st, d.sms);
-            case 256: return launch_step_queue<2, true>(s, st, d.sms);
-            case 512: return launch_step_queue<4, true>(s, st, d.sms);
-            case 1024: return launch_step_queue<8, true>(s, st, d.sms);
+            case 128: return launch_step_queue<1, true>(s, st, d);
+            case 256: return launch_step_queue<2, true>(s, st, d);
+            case 512: return launch_step_queue<4, true>(s, st, d);
+            case 1024: return launch_step_queue<8, true>(s, st, d);
             default: break;
         }
-        if (D <= 64) return launch_step_queue<1, false, true>(s, st, d.sms);
-        if (D < 128) return launch_step_queue<1, false>(s, st, d.sms);
-        if (D < 256) return launch_step_queue<2, false>(s, st, d.sms);
-        if (D < 512) return launch_step_queue<4, false>(s, st, d.sms);
-        return launch_step_queue<8, false>(s, st, d.sms);
+        if (D <= 64) return launch_step_queue<1, false, true>(s, st, d);
+        if (D < 128) return launch_step_queue<1, false>(s, st, d);
+        if (D < 256) return launch_step_queue<2, false>(s, st, d);
+        if (D < 512) return launch_step_queue<4, false>(s, st, d);
+        return launch_step_queue<8, false>(s, st, d);
     }
     switch (D) {
-        case 128: return launch_step<1, true>(s, mode, st, d.sms);
-        case 256: return launch_step<2, true>(s, mode, st, d.sms);
-        case 512: return launch_step<4, true>(s, mode, st, d.sms);
-        case 1024: return launch_step<8, true>(s, mode, st, d.sms);
+        case 128: return launch_step<1, true>(s, mode, st, d);
+        case 256: return launch_step<2, true>(s, mode, st, d);
+        case 512: return launch_step<4, true>(s, mode, st, d);
+        case 1024: return launch_step<8, true>(s, mode, st, d);
         default: break;
     }
-    if (D <= 64) return launch_step<1, false, true>(s, mode, st, d.sms);    // two rows per warp-wide load
-    if (D < 128) return launch_step<1, false>(s, mode, st, d.sms);
-    if (D < 256) return launch_step<2, false>(s, mode, st, d.sms);
-    if (D < 512) return launch_step<4, false>(s, mode, st, d.sms);
-    return launch_step<8, false>(s, mode, st, d.sms);
+    if (D <= 64) return launch_step<1, false, true>(s, mode, st, d);    // two rows per warp-wide load
+    if (D < 128) return launch_step<1, false>(s, mode, st, d);
+    if (D < 256) return launch_step<2, false>(s, mode, st, d);
+    if (D < 512) return launch_step<4, false>(s, mode, st, d);
+    return launch_step<8, false>(s, mode, st, d);
 }
 
 int cs_sim_begin(const cs_state* s, float sep, cs_stream stream) {
@@ -456,7 +456,123 @@ int cs_fps_step_lanes(const cs_state* lanes, int32_t n_lanes, uint32_t mode, cs_
     LaneSet ls;
     for (int l = 0; l < n_lanes; ++l) ls.s[l] = lanes[l];
     for (int l = n_lanes; l < CS_MAX_LANES; ++l) ls.s[l] = lanes[0];
-    return launch_lanes(ls, n_lanes, mode, (cudaStream_t)stream, d.sms);
+    return launch_lanes(ls, n_lanes, mode, (cudaStream_t)stream, d);
+}
+
+}  // extern "C"
+
+namespace {
+
+int validate_cells(const cs_state* s, const cs_cells* c) {
+    if (!c || !c->perm || !c->hp || !c->vp || !c->cell0 || !c->seg_start || !c->seg_count || !c->seg_key || !c->seg_h0 ||
+        !c->cursor || !c->work_cell || !c->work_cum || !c->meta || !c->queue) return CS_E_ARG;
+    if (c->q_cap < kCellTile || ((uintptr_t)c->queue & 7u)) return CS_E_ARG;
+    if (s->N_local <= 0) return CS_E_ARG;
+    if (s->cap > 65536) return CS_E_RANGE;                      // the selection kernel takes 64 cells per thread
+    if (c->slots >= (int64_t)1 << 31 || c->slots < s->N_local + s->cap * (int64_t)kCellTile) return CS_E_RANGE;
+    if ((((uintptr_t)c->perm | (uintptr_t)c->hp | (uintptr_t)c->vp) & 15u) || ((uintptr_t)c->meta & 7u)) return CS_E_ALIGN;
+    if (!(c->row_norm_max >= 0.0f)) return CS_E_ARG;
+    return CS_OK;
+}
+
+template <int CPL, bool FULL, bool HALF = false>
+int launch_step_cells(const cs_state* s, const cs_cells* c, cudaStream_t st, const DevInfo& dv) {
+    static thread_local KernelTune tune_scan, tune_eval;
+    int per_scan = 0, per_eval = 0;
+    int rc = tune_kernel(cells_scan_kernel<CPL, FULL, HALF>, tune_scan, dv.dev, 0, kThreads, &per_scan);
+    if (rc) return rc;
+    rc = tune_kernel(cells_eval_kernel<CPL, FULL, HALF>, tune_eval, dv.dev, 0, kThreads, &per_eval);
+    if (rc) return rc;
+    // persistent grids: the numbers of tiles and of queued rows are only known on the device
+    const int64_t tiles = (s->N_local + kCellTile - 1) / kCellTile + 1;
+    const int64_t want_scan = (tiles + kWarps - 1) / kWarps, cap_scan = (int64_t)dv.sms * per_scan;
+    cells_scan_kernel<CPL, FULL, HALF><<<(int)(want_scan < cap_scan ? want_scan : cap_scan), kThreads, 0, st>>>(*s, *c);
+    rc = check_launch();
+    if (rc) return rc;
+    const int64_t want_eval = ((int64_t)c->q_cap + kThreads - 1) / kThreads, cap_eval = (int64_t)dv.sms * per_eval;
+    cells_eval_kernel<CPL, FULL, HALF><<<(int)(want_eval < cap_eval ? want_eval : cap_eval), kThreads, 0, st>>>(*s, *c);
+    return check_launch();
+}
+
+}  // namespace
+
+extern "C" {
+
+int cs_cells_build(const cs_state* s, const cs_cells* c, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    rc = validate_cells(s, c);
+    if (rc) return rc;
+    DevInfo d = device_info();
+    if (!d.ok) return CS_E_DEVICE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemsetAsync(c->seg_count, 0, (size_t)s->cap * sizeof(int32_t), st) != cudaSuccess) {
+        g_last_cuda = cudaGetLastError();
+        return CS_E_LAUNCH;
+    }
+    const int bins = (int)(s->cap < kCellBinsSmem ? s->cap : kCellBinsSmem);
+    const size_t smem = (size_t)bins * sizeof(int);
+    static thread_local KernelTune tune_hist, tune_scatter;
+    int per_hist = 0, per_scatter = 0;
+    rc = tune_kernel(cells_hist_kernel, tune_hist, d.dev, smem, kThreads, &per_hist);
+    if (rc) return rc;
+    rc = tune_kernel(cells_scatter_kernel, tune_scatter, d.dev, smem, kThreads, &per_scatter);
+    if (rc) return rc;
+    const int64_t row_blocks = (s->N_local + 4 * kThreads - 1) / (4 * kThreads);
+    const int64_t lim_hist = (int64_t)d.sms * per_hist;
+    cells_hist_kernel<<<(int)(row_blocks < lim_hist ? row_blocks : lim_hist), kThreads, smem, st>>>(*s, *c);
+    cells_offsets_kernel<<<1, 1024, 0, st>>>(*s, *c);
+    int rows_per_block = 4 * bins;
+    rows_per_block = rows_per_block < 16384 ? 16384 : (rows_per_block > (1 << 18) ? (1 << 18) : rows_per_block);
+    const int64_t chunks = (s->N_local + rows_per_block - 1) / rows_per_block;
+    const int64_t lim_scatter = (int64_t)d.sms * per_scatter;
+    cells_scatter_kernel<<<(int)(chunks < lim_scatter ? chunks : lim_scatter), kThreads, smem, st>>>(*s, *c, rows_per_block);
+    const int64_t cell_blocks = (s->cap + kWarps - 1) / kWarps;
+    const int64_t lim = (int64_t)d.sms * 8;
+    cells_pad_kernel<<<(int)(cell_blocks < lim ? cell_blocks : lim), kThreads, 0, st>>>(*s, *c);
+    const int64_t tile_blocks = (c->slots / kCellTile + kWarps - 1) / kWarps;
+    cells_keys_kernel<<<(int)(tile_blocks < lim ? tile_blocks : lim), kThreads, 0, st>>>(*s, *c);
+    const int64_t h0_blocks = (s->cap + kThreads - 1) / kThreads;
+    cells_h0_kernel<<<(int)(h0_blocks < lim ? h0_blocks : lim), kThreads, 0, st>>>(*s, *c);
+    return check_launch();
+}
+
+int cs_cells_select(const cs_state* s, const cs_cells* c, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    rc = validate_cells(s, c);
+    if (rc) return rc;
+    // rounding-error bound of one computed squared distance, relative to the sum of the two squared
+    // norms: D products and sums in the dot product, D in each norm, a few more in the final formula;
+    // the factor 4 is slack
+    const double g = 4.0 * ((double)s->D + 32.0) * 5.9604644775390625e-8;
+    cells_select_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(*s, *c, g);
+    return check_launch();
+}
+
+int cs_fps_step_cells(const cs_state* s, const cs_cells* c, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    rc = validate_cells(s, c);
+    if (rc) return rc;
+    const int D = s->D;
+    if ((D & 3) != 0 || D > 1024 || (s->flags & CS_F_ELEMENT_ORDER)) return CS_E_ARG;
+    if (((uintptr_t)s->h | (uintptr_t)s->voronoi) & 3u) return CS_E_ALIGN;
+    DevInfo d = device_info();
+    if (!d.ok) return CS_E_DEVICE;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (D) {
+        case 128: return launch_step_cells<1, true>(s, c, st, d);
+        case 256: return launch_step_cells<2, true>(s, c, st, d);
+        case 512: return launch_step_cells<4, true>(s, c, st, d);
+        case 1024: return launch_step_cells<8, true>(s, c, st, d);
+        default: break;
+    }
+    if (D <= 64) return launch_step_cells<1, false, true>(s, c, st, d);
+    if (D < 128) return launch_step_cells<1, false>(s, c, st, d);
+    if (D < 256) return launch_step_cells<2, false>(s, c, st, d);
+    if (D < 512) return launch_step_cells<4, false>(s, c, st, d);
+    return launch_step_cells<8, false>(s, c, st, d);
 }
 
 }  // extern "C"
@@ -474,7 +590,6 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[CS_NOALLOC_SCRA
 
 namespace {
 
-constexpr int kMaxDevices = 64;
 unsigned char* g_noalloc_ptr[kMaxDevices] = {nullptr};
 
 // Device address of g_noalloc_scratch on the CURRENT device.  In host code the array's name is

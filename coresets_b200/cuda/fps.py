@@ -56,7 +56,7 @@ def fps(
     X = X.contiguous()
     norms = _engine.row_norms(X)                       # in X's own dtype, as fps.py:34 does
     X32, element_order = _engine.engine_matrix(X)
-    eng = _engine.ShardEngine(X32, norms, n_to_select, element_order=element_order)
+    eng = _engine.ShardEngine(X32, norms, n_to_select, element_order=element_order, cells=True)
     eng.init_state()
     for idx in seed_list:
         eng.pick_forced(idx)

@@ -99,7 +99,7 @@ def fps_sharded(
     X32, element_order = _engine.engine_matrix(X_local)
     eng = _engine.ShardEngine(
         X32, norms_local, n_to_select, shard_offset=layout.shard_offset,
-        world_size=world_size, group=None, element_order=element_order,
+        world_size=world_size, group=None, element_order=element_order, cells=True,
     )
     eng.init_state()
 

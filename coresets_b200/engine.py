@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist
 
 from . import _native
-from ._native import CsState, CtlView, MODE_DENSE, MODE_PRUNE, RULE_NONE, XCHG_GATHER, XCHG_PEER
+from ._native import CsCells, CsState, CtlView, MODE_DENSE, MODE_PRUNE, RULE_NONE, XCHG_GATHER, XCHG_PEER
 
 _NORM_CHUNK_ELEMS = 1 << 28  # elements of the X*X temporary per chunk (1 GiB of fp32)
 
@@ -84,6 +84,28 @@ def exchange_mode() -> str:
     return m
 
 
+def _cells_env() -> bool:
+    """``CORESETS_B200_CELLS=0`` keeps every pick on the full scan of h / voronoi."""
+    return bool(int(os.environ.get("CORESETS_B200_CELLS", "1")))
+
+
+# Cell index (see cs_cells in include/coresets_b200.h): the first picks run on the scan kernels,
+# the index is built when this many centres exist and rebuilt every time their number has doubled.
+# Each constant can be overridden through the environment (tests build tiny indexes often).
+def _knob(name: str, default, kind=int):
+    return kind(os.environ.get("CORESETS_B200_" + name, default))
+
+
+_CELLS_FIRST_BUILD = 64          # CELLS_FIRST_BUILD
+_CELLS_GROWTH = 2.0              # CELLS_GROWTH
+_CELLS_MIN_ROWS = 1 << 18        # CELLS_MIN_ROWS: below this a full scan costs less than the launches of an indexed pick
+_CELLS_PROBE_PICKS = 32          # CELLS_PROBE_PICKS: picks after a build before the visited share is read back
+_CELLS_GIVE_UP_SHARE = 0.2       # CELLS_GIVE_UP_SHARE: above this share of the slots per pick the scan kernel wins
+_CELLS_LIVE_GATE = 0.1           # CELLS_LIVE_GATE: no index while a pick still evaluates this share of the rows
+_EARLY_DENSE_PICKS = 24          # EARLY_DENSE_PICKS: nearly every row passes the triangle test this early, so
+                                 # X is streamed with the bulk-copy ring
+
+
 def _graph_picks() -> int:
     return max(1, int(os.environ.get("CORESETS_B200_GRAPH_PICKS", "32")))
 
@@ -100,7 +122,7 @@ class ShardEngine:
     def __init__(self, X_local: torch.Tensor, norms: torch.Tensor, cap: int, *, shard_offset: int = 0,
                  world_size: int = 1, group=None, mode: Optional[int] = None,
                  h: Optional[torch.Tensor] = None, voronoi: Optional[torch.Tensor] = None,
-                 record: bool = True, element_order: bool = False):
+                 record: bool = True, element_order: bool = False, cells: bool = False):
         if X_local.dim() != 2:
             raise ValueError(f"X_local must be 2-D, got shape {tuple(X_local.shape)}")
         if X_local.dtype != torch.float32:
@@ -147,6 +169,24 @@ class ShardEngine:
                                      pin_memory=self.on_cuda)
         self._graphs = {}
         self.state = self._make_state()
+        # cell index: only for plain farthest-point runs on the device (the caller asks for it)
+        self.n_host: Optional[int] = None      # picks committed so far, when the host can tell
+        self._first_build = max(1, _knob("CELLS_FIRST_BUILD", _CELLS_FIRST_BUILD))
+        self._growth = max(1.05, _knob("CELLS_GROWTH", _CELLS_GROWTH, float))
+        self._probe_picks = max(1, _knob("CELLS_PROBE_PICKS", _CELLS_PROBE_PICKS))
+        self._give_up_share = _knob("CELLS_GIVE_UP_SHARE", _CELLS_GIVE_UP_SHARE, float)
+        self._early_dense = max(0, _knob("EARLY_DENSE_PICKS", _EARLY_DENSE_PICKS))
+        self._live_gate = _knob("CELLS_LIVE_GATE", _CELLS_LIVE_GATE, float)
+        self.cells_enabled = bool(
+            cells and self.on_cuda and _cells_env() and self.mode == MODE_PRUNE and not self.element_order
+            and self.D % 4 == 0 and self.D <= 1024 and self.cap <= 65536
+            and self.N_local >= _knob("CELLS_MIN_ROWS", _CELLS_MIN_ROWS)
+            and self.N_local + self.cap * _native.CELL_TILE < 2 ** 31)
+        self._cells: Optional[CsCells] = None
+        self._cells_ok = False                 # the index mirrors h / voronoi
+        self._cells_next_build = 0
+        self._cells_scan_until = 0             # an epoch the index lost: scan kernels up to this pick count
+        self.cells_log = []                    # (built at, visited share of the probe) per build
 
     # -- plumbing ------------------------------------------------------------------------------
     def _open_peer_windows(self) -> None:
@@ -201,6 +241,7 @@ class ShardEngine:
             self.voronoi = voronoi
         self.state = self._make_state()
         self._graphs.clear()
+        self._cells_ok = False
 
     def _stream(self) -> int:
         return torch.cuda.current_stream(self.device).cuda_stream if self.on_cuda else 0
@@ -208,9 +249,13 @@ class ShardEngine:
     # -- single launches -------------------------------------------------------------------------
     def init_state(self) -> None:
         self.native.init_state(self.state, self._stream())
+        self.n_host = 0
+        self._cells_ok = False
 
     def reset_ctl(self, n_sel: int) -> None:
         self.native.reset_ctl(self.state, int(n_sel), self._stream())
+        self.n_host = int(n_sel)
+        self._cells_ok = False
 
     def _before_publish(self) -> None:
         # peer exchange: sequence s+1 may only be published once every peer's s has been seen
@@ -245,22 +290,36 @@ class ShardEngine:
     def step(self, mode: Optional[int] = None) -> None:
         self.native.fps_step(self.state, self.mode if mode is None else int(mode), self._stream())
         self._unconsumed = True
+        self._cells_ok = False             # h changed behind the index
+        if self.n_host is not None:
+            self.n_host += 1
 
     # -- picks -------------------------------------------------------------------------------------
-    def _pick_body(self, rules: int) -> None:
+    def _pick_body(self, rules: int, how=None) -> None:
+        """One pick.  ``how``: None = the engine's mode, an int = that step mode, "cells" = through
+        the cell index."""
         self.exchange()
         self.commit(rules)
-        self.step()
+        if how == "cells":
+            st = self._stream()
+            self.native.cells_select(self.state, self._cells, st)
+            self.native.fps_step_cells(self.state, self._cells, st)
+            self._unconsumed = True
+            if self.n_host is not None:
+                self.n_host += 1
+        else:
+            self.step(how)
 
     def pick_forced(self, global_idx: int, val: float = float("inf"), rules: int = RULE_NONE) -> None:
         """Commit a prescribed row as the next centre and run its update."""
         self.force_pick(global_idx, val)
         self._pick_body(rules)
 
-    def _graph(self, n: int, rules: int):
-        key = (n, rules, self.mode)
+    def _graph(self, n: int, rules: int, how=None):
+        key = (n, rules, self.mode if how is None else how)
         g = self._graphs.get(key)
         if g is None:
+            n_before, ok_before = self.n_host, self._cells_ok
             # Nothing may be in flight while the stream captures: with collectives in the body the
             # process group's watchdog thread polls the events of earlier eager collectives, and
             # an event query from another thread invalidates a capture in the default "global"
@@ -269,39 +328,146 @@ class ShardEngine:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, capture_error_mode="thread_local"):
                 for _ in range(n):
-                    self._pick_body(rules)
+                    self._pick_body(rules, how)
             self._graphs[key] = g
+            self.n_host, self._cells_ok = n_before, ok_before      # capturing ran nothing
         return g
 
     _UNITS = (32, 16, 8, 4, 2, 1)
+
+    def _units(self, n: int):
+        """Binary decomposition of ``n`` picks into the graph sizes (largest first)."""
+        top = min(_graph_picks(), self._UNITS[0])
+        for unit in self._UNITS:
+            if unit <= top:
+                while n >= unit:
+                    yield unit
+                    n -= unit
 
     def prepare(self, n: int, rules: int = RULE_NONE) -> None:
         """Capture (without running) the graphs ``run_picks(n)`` will replay."""
         if not (self.on_cuda and _graphs_enabled()):
             return
-        top = min(_graph_picks(), self._UNITS[0])
-        for unit in self._UNITS:
-            if unit <= top and n >= unit:
-                self._graph(unit, rules)
-                n %= unit
+        kinds = [None]
+        if self._uses_cells(rules):
+            self._alloc_cells()
+            kinds.append("cells")
+            if self.n_host < self._early_dense:
+                kinds.append(MODE_DENSE)
+        for how in kinds:
+            for unit in set(self._units(n)):
+                self._graph(unit, rules, how)
+
+    def _replay(self, n: int, rules: int, how) -> None:
+        """Enqueue ``n`` picks of one kind: graph replays, or single launches when graphs are off."""
+        if self.on_cuda and _graphs_enabled():
+            for unit in self._units(n):
+                self._graph(unit, rules, how).replay()
+                self._unconsumed = True
+                if self.n_host is not None:
+                    self.n_host += unit
+                if how != "cells":
+                    self._cells_ok = False
+            return
+        for _ in range(n):
+            self._pick_body(rules, how)
+
+    def _uses_cells(self, rules: int) -> bool:
+        return self.cells_enabled and self.n_host is not None and rules == RULE_NONE
 
     def run_picks(self, n: int, rules: int = RULE_NONE) -> None:
-        """Enqueue ``n`` farthest-point picks.  No host synchronisation happens here: the picks
-        are replayed from CUDA graphs of 32, 16, ... 1 picks (binary decomposition of ``n``)."""
+        """Enqueue ``n`` farthest-point picks, replayed from CUDA graphs of 32, 16, ... 1 picks
+        (binary decomposition of ``n``).  Without the cell index nothing here synchronises with the
+        host.  With it (plain farthest-point runs) the picks are cut at the points where the
+        index is built (64 centres, then every doubling), and once per build the host reads back
+        how much of the index the first picks visited, to fall back to the scan kernels on data
+        the index does not help."""
         n = int(n)
         if n <= 0:
             return
-        if self.on_cuda and _graphs_enabled():
-            top = min(_graph_picks(), self._UNITS[0])
-            for unit in self._UNITS:
-                if unit > top:
-                    continue
-                while n >= unit:
-                    self._graph(unit, rules).replay()
-                    self._unconsumed = True
-                    n -= unit
-        for _ in range(n):
-            self._pick_body(rules)
+        if not self._uses_cells(rules):
+            self._replay(n, rules, None)
+            return
+        while n > 0:
+            cur = self.n_host
+            if cur < self._early_dense:
+                m = min(n, self._early_dense - cur)
+                self._replay(m, rules, MODE_DENSE)
+            elif cur < max(self._first_build, self._cells_scan_until):
+                m = min(n, max(self._first_build, self._cells_scan_until) - cur)
+                self._replay(m, rules, None)
+            else:
+                if not self._cells_ok or cur >= self._cells_next_build:
+                    # an index pays once a pick leaves most rows alone; while the last pick still
+                    # evaluated a large share of them the scan kernels stay (one read-back)
+                    if self.read_ctl().live_rows > self._live_gate * self.N_local:
+                        self._cells_scan_until = max(cur + 16, int(cur * 1.25))
+                        continue
+                    self._build_cells()
+                m = min(n, self._cells_next_build - cur)
+                if self._cells_probe_left > 0:
+                    m = min(m, self._cells_probe_left)
+                    self._replay(m, rules, "cells")
+                    self._cells_probe_left -= m
+                    if self._cells_probe_left == 0:
+                        self._judge_cells()
+                else:
+                    self._replay(m, rules, "cells")
+            n -= m
+
+    # -- cell index ----------------------------------------------------------------------------------
+    def _alloc_cells(self) -> None:
+        if self._cells is not None:
+            return
+        dev, i32 = self.device, torch.int32
+        slots = (self.N_local + self.cap * _native.CELL_TILE + 3) & ~3
+        bufs = dict(
+            perm=torch.empty(slots, dtype=i32, device=dev), hp=torch.empty(slots, dtype=torch.float32, device=dev),
+            vp=torch.empty(slots, dtype=i32, device=dev), cell0=torch.empty(self.N_local, dtype=i32, device=dev),
+            seg_start=torch.zeros(self.cap + 1, dtype=i32, device=dev), seg_count=torch.zeros(self.cap, dtype=i32, device=dev),
+            seg_key=torch.zeros(self.cap, dtype=torch.int64, device=dev), seg_h0=torch.zeros(self.cap, dtype=torch.float32, device=dev),
+            cursor=torch.zeros(self.cap, dtype=i32, device=dev), work_cell=torch.zeros(self.cap, dtype=i32, device=dev),
+            work_cum=torch.zeros(self.cap, dtype=i32, device=dev),
+            meta=torch.zeros(_native.CELLS_META_BYTES // 8, dtype=torch.int64, device=dev))
+        # rows of one pick that wait for a distance: a quarter of the shard is far more than a pick
+        # needs once the index is in use (the kernels stay correct when it overflows, only slower)
+        q_cap = max(_native.CELL_TILE, _knob("CELLS_QUEUE", max(1 << 16, self.N_local // 4)))
+        bufs["queue"] = torch.empty((q_cap, 2), dtype=i32, device=dev)
+        c = CsCells()
+        for name, t in bufs.items():
+            setattr(c, name, t.data_ptr())
+        c.slots = slots
+        c.q_cap = q_cap
+        c.row_norm_max = float(self.norms.max().item())           # one read-back, at the first build
+        self._cells_bufs = bufs
+        self._cells_meta_host = torch.empty(_native.CELLS_META_BYTES // 8, dtype=torch.int64, pin_memory=True)
+        self._cells = c
+
+    def _build_cells(self) -> None:
+        self._alloc_cells()
+        cur = self.n_host
+        self.native.cells_build(self.state, self._cells, self._stream())
+        self._cells_ok = True
+        self._cells_built_at = cur
+        self._cells_next_build = max(cur + min(self._first_build, 64), int(cur * self._growth))
+        self._cells_probe_left = self._probe_picks
+
+    def read_cells_meta(self) -> "_native.CellsMetaView":
+        """Copy the index's statistics block to the host (synchronises the current stream)."""
+        self._cells_meta_host.copy_(self._cells_bufs["meta"], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        view = _native.CellsMetaView()
+        ctypes.memmove(ctypes.addressof(view), self._cells_meta_host.data_ptr(), _native.CELLS_META_BYTES)
+        return view
+
+    def _judge_cells(self) -> None:
+        """After the first picks on a fresh index: if they visited most of it, the data does not
+        separate into cells (or not yet) and the scan kernels take the rest of this epoch."""
+        mv = self.read_cells_meta()
+        share = mv.visited_slots / max(1, mv.picks) / max(1, mv.total_slots)
+        self.cells_log.append((self._cells_built_at, round(share, 4)))
+        if share > self._give_up_share:
+            self._cells_scan_until = self._cells_next_build
 
     # -- several states in one pass over X ("lanes") --------------------------------------------------
     @staticmethod
@@ -314,6 +480,8 @@ class ShardEngine:
         e0.native.fps_step_lanes(arr, len(engines), m, e0._stream())
         for e in engines:
             e._unconsumed = True
+            e._cells_ok = False
+            e.n_host = None
 
     @staticmethod
     def run_lane_picks(engines, n: int, rules: int) -> None:
@@ -342,6 +510,8 @@ class ShardEngine:
         g.replay()
         for e in engines:
             e._unconsumed = True
+            e._cells_ok = False
+            e.n_host = None
 
     def kth_largest_live(self, k: int):
         """``(value, n_alive)``: the exact ``k``-th largest entry of this engine's ``h`` among the

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define CS_ABI_VERSION 6
+#define CS_ABI_VERSION 7
 
 #if defined(__GNUC__)
 #define CS_API __attribute__((visibility("default")))
@@ -256,6 +256,67 @@ CS_API int cs_pool_argmax(const float* h, const int64_t* pool, int64_t n_pool, i
  * Replaces voronoi_update_lanes_kernel (kernels/multi.cu:569-708).
  */
 CS_API int cs_fps_step_lanes(const cs_state* lanes, int32_t n_lanes, uint32_t mode, cs_stream stream);
+
+/*
+ * Cell index: the rows of a shard grouped by the centre that owned them when the index was built.
+ * No counterpart in the reference, whose per-pick kernel reads h and voronoi of EVERY row
+ * (kernels/warp.cu:54-100).  With the index a pick reads only the cells whose rows can possibly
+ * change: cell A is left alone when the triangle inequality through its centre, widened by a bound
+ * on the rounding error of the distance formula, proves that every row in it keeps its h.  Rows of
+ * the cells that remain are tested one by one with the reference's own predicate
+ * (dSL_quarter[voronoi] >= h) and evaluated with the reference's arithmetic, so h, voronoi and the
+ * picks are bit-identical to cs_fps_step.  h / voronoi stay authoritative in row order (every
+ * update is written to both copies); the index goes stale whenever something else changes h.
+ *
+ * Memory, all owned by the caller: slots = N_local + cap * CS_CELL_TILE entries of perm / hp / vp,
+ * N_local of cell0, cap (+1) of the per-cell arrays, CS_CELLS_META_BYTES of meta, q_cap pairs of queue.
+ */
+#define CS_CELL_TILE 256         /* segments are padded to whole tiles of this many slots */
+#define CS_CELLS_META_BYTES 128
+typedef struct cs_cells {
+    int32_t* perm;        /* [slots] local row held by each slot, -1 = padding                */
+    float* hp;            /* [slots] copy of h in slot order (-inf on padding)                */
+    int32_t* vp;          /* [slots] copy of voronoi in slot order                            */
+    int32_t* cell0;       /* [N_local] cell of each row when the index was built              */
+    int64_t slots;        /* capacity of perm / hp / vp (< 2^31)                               */
+    int32_t* seg_start;   /* [cap + 1] first slot of each cell                                 */
+    int32_t* seg_count;   /* [cap] rows of each cell when the index was built                  */
+    uint64_t* seg_key;    /* [cap] arg-max key over the cell's slots                           */
+    float* seg_h0;        /* [cap] largest h of the cell when the index was built              */
+    int32_t* cursor;      /* [cap] scratch of the build                                        */
+    int32_t* work_cell;   /* [cap] cells the pick in flight visits                             */
+    int32_t* work_cum;    /* [cap] running number of chunks over work_cell                     */
+    void* meta;           /* CS_CELLS_META_BYTES, see cs_cells_meta_view                       */
+    void* queue;          /* [q_cap] pairs of int32 (slot, cell): rows waiting for a distance  */
+    float row_norm_max;   /* an upper bound of norms[0..N_local) (error bound of the skip test) */
+    int32_t q_cap;        /* entries of queue (>= CS_CELL_TILE); rows beyond it are evaluated
+                             by the scanning kernel itself, slower but with the same result    */
+} cs_cells;
+
+/* Host-visible mirror of cs_cells.meta. */
+typedef struct cs_cells_meta_view {
+    int32_t n_cells;         /* cells (= centres) when the index was built                      */
+    int32_t n_work;          /* cells visited by the last pick                                  */
+    int32_t n_chunks;        /* tiles of CS_CELL_TILE slots visited by the last pick             */
+    int32_t total_slots;     /* slots in use                                                    */
+    uint64_t visited_slots;  /* slots visited, summed over the picks since the build            */
+    uint64_t picks;          /* picks since the build                                           */
+    uint32_t q_count;        /* rows the last pick queued for evaluation                        */
+    uint32_t q_inline;       /* rows the last pick evaluated outside the queue (queue full)     */
+    uint8_t reserved[CS_CELLS_META_BYTES - 40];
+} cs_cells_meta_view;
+
+/* Build the index from the current h / voronoi with one cell per committed centre (n_sel of them).
+ * Requires n_sel >= 1.  Several launches, no host synchronisation. */
+CS_API int cs_cells_build(const cs_state* s, const cs_cells* c, cs_stream stream);
+
+/* One pick with the index, after cs_commit_bound: choose the cells to visit ... */
+CS_API int cs_cells_select(const cs_state* s, const cs_cells* c, cs_stream stream);
+
+/* ... and run the update over them (two launches: scan the visited cells, then evaluate the rows
+ * that need a distance); same effect on h, voronoi, the control block and the candidate pack as
+ * cs_fps_step(CS_MODE_PRUNE).  Row widths: D % 4 == 0, D <= 1024. */
+CS_API int cs_fps_step_cells(const cs_state* s, const cs_cells* c, cs_stream stream);
 
 /*
  * cs_fps_step without any caller-provided scratch and without any allocation.  No counterpart
