@@ -79,3 +79,22 @@ def test_fps_sharded_peer_exchange_multi(tmp_path, world):
         pytest.skip(f"needs {world} GPUs")
     _launch(world, dict(cases=_cases(world), out_dir=str(tmp_path)),
             extra_env={"CORESETS_B200_EXCHANGE": "p2p", "CORESETS_B200_XCHG_TIMEOUT_MS": "5000"})
+
+
+CELLS_EAGER = {"CORESETS_B200_CELLS_MIN_ROWS": "1", "CORESETS_B200_CELLS_FIRST_BUILD": "3", "CORESETS_B200_CELLS_GROWTH": "1.4",
+               "CORESETS_B200_EARLY_DENSE_PICKS": "2", "CORESETS_B200_CELLS_GIVE_UP_SHARE": "2.0",
+               "CORESETS_B200_CELLS_PROBE_PICKS": "5", "CORESETS_B200_CELLS_LIVE_GATE": "2.0"}
+
+
+def test_fps_sharded_cell_index_world1(tmp_path):
+    """The cell index inside fps_sharded (tiny indexes, rebuilt often) on a one-rank NCCL group."""
+    _launch(1, dict(cases=_cases(1), out_dir=str(tmp_path)), extra_env=CELLS_EAGER)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("xchg", ["nccl", "p2p"])
+def test_fps_sharded_cell_index_multi(tmp_path, world, xchg):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _launch(world, dict(cases=_cases(world), out_dir=str(tmp_path)),
+            extra_env=dict(CELLS_EAGER, CORESETS_B200_EXCHANGE=xchg, CORESETS_B200_XCHG_TIMEOUT_MS="5000"))
