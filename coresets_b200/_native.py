@@ -36,7 +36,7 @@ EXPORTS = (
     "cs_version", "cs_error_string", "cs_last_cuda_error", "cs_device_check", "cs_init_state",
     "cs_reset_ctl", "cs_force_pick", "cs_commit_bound", "cs_fps_step", "cs_sim_begin",
     "cs_sim_final_check", "cs_xchg_window_words", "cs_xchg_wait", "cs_scan_argmax", "cs_fps_step_lanes", "cs_fps_step_noalloc",
-    "cs_select_kth_largest", "cs_pool_argmax", "cs_cells_build", "cs_cells_select", "cs_fps_step_cells",
+    "cs_select_kth_largest", "cs_pool_argmax", "cs_cells_build", "cs_cells_select", "cs_fps_step_cells", "cs_force_pick_list",
 )
 
 
@@ -177,6 +177,7 @@ class Native:
             ("cs_init_state", [sp, vp]),
             ("cs_reset_ctl", [sp, ctypes.c_int32, vp]),
             ("cs_force_pick", [sp, ctypes.c_int64, ctypes.c_float, vp]),
+            ("cs_force_pick_list", [sp, vp, ctypes.c_float, vp]),
             ("cs_commit_bound", [sp, ctypes.c_uint32, vp]),
             ("cs_fps_step", [sp, ctypes.c_uint32, vp]),
             ("cs_sim_begin", [sp, ctypes.c_float, vp]),
@@ -222,6 +223,9 @@ class Native:
 
     def force_pick(self, s: CsState, global_idx: int, val: float, stream: int) -> None:
         self._check(self.lib.cs_force_pick(ctypes.byref(s), global_idx, val, stream), "cs_force_pick")
+
+    def force_pick_list(self, s: CsState, list_ptr: int, val: float, stream: int) -> None:
+        self._check(self.lib.cs_force_pick_list(ctypes.byref(s), list_ptr, val, stream), "cs_force_pick_list")
 
     def commit_bound(self, s: CsState, rules: int, stream: int) -> None:
         self._check(self.lib.cs_commit_bound(ctypes.byref(s), rules, stream), "cs_commit_bound")

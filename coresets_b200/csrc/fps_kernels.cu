@@ -279,6 +279,14 @@ int cs_force_pick(const cs_state* s, int64_t global_idx, float val, cs_stream st
     return check_launch();
 }
 
+int cs_force_pick_list(const cs_state* s, const int64_t* list, float val, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    if (!list) return CS_E_ARG;
+    force_pick_list_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(*s, list, val);
+    return check_launch();
+}
+
 int cs_commit_bound(const cs_state* s, uint32_t rules, cs_stream stream) {
     int rc = validate(s);
     if (rc) return rc;

@@ -24,7 +24,7 @@ __global__ void reset_ctl_kernel(Ctl* ctl, int n_sel) {
     if (threadIdx.x == 0) ctl->n_sel = n_sel;
 }
 
-__global__ void force_pick_kernel(const cs_state s, const int64_t gidx, const float val) {
+__device__ __forceinline__ void force_pick_body(const cs_state& s, const int64_t gidx, const float val) {
     Ctl* ctl = reinterpret_cast<Ctl*>(s.ctl);
     const int i = ctl->n_sel;
     const int64_t l = gidx - s.shard_offset;
@@ -35,6 +35,17 @@ __global__ void force_pick_kernel(const cs_state s, const int64_t gidx, const fl
         if (s.world_size <= 1 && !owner) ctl->status = ST_FORCE_NOT_OWNED;
     }
     if (s.world_size > 1) publish_candidate(s, ctl, k, l);
+}
+
+__global__ void force_pick_kernel(const cs_state s, const int64_t gidx, const float val) { force_pick_body(s, gidx, val); }
+
+// The same with the row taken from a device list at the position of the pick counter, so that a
+// run of prescribed picks (a resumed checkpoint) can be replayed from a CUDA graph.
+__global__ void force_pick_list_kernel(const cs_state s, const int64_t* __restrict__ list, const float val) {
+    const Ctl* ctl = reinterpret_cast<const Ctl*>(s.ctl);
+    const int i = ctl->n_sel;
+    if (i >= s.cap) return;                                // the commit kernel reports the overflow
+    force_pick_body(s, list[i], val);
 }
 
 __global__ void sim_begin_kernel(Ctl* ctl, float sep) {

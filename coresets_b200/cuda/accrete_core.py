@@ -646,6 +646,7 @@ class AccreteDriver:
         """`<prefix>_kKK.npy`, `<prefix>_kKK_sep.npy`, then `<prefix>_latest.txt` = "k"
         (sharded.py:754-775)."""
         p = self.checkpoint_path
+        self.E.check_status()     # a device-side time-out leaves garbage picks: raise, do not publish them
         ids = np.asarray(self.selected[:target_size], dtype=np.int64)
         self._save(f"{p}_k{k:02d}.npy", ids)
         self._save(f"{p}_k{k:02d}_sep.npy", np.asarray([self.sep], dtype=np.float64))
@@ -673,6 +674,7 @@ class AccreteDriver:
         if self.checkpoint_path is None or self.layout.rank != 0:
             return
         p = self.checkpoint_path
+        self.E.check_status()
         self._save(f"{p}_mid.npy", np.asarray(self.selected, dtype=np.int64))
         self._save(f"{p}_mid_sep.npy", np.asarray([self.sep], dtype=np.float64))
         self._save_text(f"{p}_latest.txt", f"{k} {n}\n")

@@ -138,10 +138,10 @@ def fps_sharded(
                 f"world_size={world_size}  host={socket.gethostname()}"
             )
         t_resume = time.time()
-        for g in selected_prev.tolist():
-            if not 0 <= g < n_global:
-                raise ValueError(f"resume checkpoint holds row {g}, outside [0, N_global={n_global})")
-            eng.pick_forced(int(g))
+        bad = selected_prev[(selected_prev < 0) | (selected_prev >= n_global)]
+        if bad.size:
+            raise ValueError(f"resume checkpoint holds row {int(bad[0])}, outside [0, N_global={n_global})")
+        eng.run_forced(selected_prev)
         if chatty:
             eng.read_ctl()
             print(f"  resume state rebuilt in {time.time() - t_resume:.1f}s (replayed {k_prev:,} picks)")
@@ -189,6 +189,7 @@ def fps_sharded(
                 f"({rate:>7.1f} pick/s, eps={math.sqrt(max(best_val, 0.0)):.4e}, cum {elapsed:.1f}s)"
             )
         if ev in ckpt_steps and rank == 0 and checkpoint_path is not None:
+            eng.check_status()        # a device-side time-out leaves garbage picks: raise, do not publish them
             _write_checkpoint(checkpoint_path, ev, eng.selected, host_eps(ev + 1))
     eng.run_picks(n_to_select - pos)
     eng.check_status()

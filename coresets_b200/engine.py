@@ -298,6 +298,11 @@ class ShardEngine:
     def _pick_body(self, rules: int, how=None) -> None:
         """One pick.  ``how``: None = the engine's mode, an int = that step mode, "cells" = through
         the cell index."""
+        if how == "forced":
+            if self.world_size > 1 and self.xchg == XCHG_PEER:
+                self.native.xchg_wait(self.state, self._stream())     # see _before_publish
+            self.native.force_pick_list(self.state, self._forced_list.data_ptr(), float("inf"), self._stream())
+            how = None
         self.exchange()
         self.commit(rules)
         if how == "cells":
@@ -314,6 +319,25 @@ class ShardEngine:
         """Commit a prescribed row as the next centre and run its update."""
         self.force_pick(global_idx, val)
         self._pick_body(rules)
+
+    def run_forced(self, indices, rules: int = RULE_NONE) -> None:
+        """Commit the prescribed global rows ``indices`` one after the other as the next centres, each
+        with its update -- ``pick_forced`` for a whole list.  On the device the rows are read from a
+        list indexed by the pick counter, so the run replays from CUDA graphs like free picks
+        (a resumed checkpoint of 16 384 picks is 512 graph replays instead of 65 536 host calls)."""
+        idx = [int(v) for v in (indices.tolist() if hasattr(indices, "tolist") else indices)]
+        if not idx:
+            return
+        if not (self.on_cuda and _graphs_enabled() and self.n_host is not None):
+            for g in idx:
+                self.pick_forced(g, rules=rules)
+            return
+        if self.n_host + len(idx) > self.cap:
+            raise ValueError(f"{len(idx)} forced picks after {self.n_host} exceed the capacity {self.cap}")
+        if not hasattr(self, "_forced_list"):
+            self._forced_list = torch.zeros(self.cap, dtype=torch.int64, device=self.device)
+        self._forced_list[self.n_host : self.n_host + len(idx)] = torch.tensor(idx, dtype=torch.int64).to(self.device)
+        self._replay(len(idx), rules, "forced")
 
     def _graph(self, n: int, rules: int, how=None):
         key = (n, rules, self.mode if how is None else how)

@@ -163,6 +163,15 @@ CS_API int cs_reset_ctl(const cs_state* s, int32_t n_sel, cs_stream stream);
 CS_API int cs_force_pick(const cs_state* s, int64_t global_idx, float val, cs_stream stream);
 
 /*
+ * cs_force_pick with the row read on the device: the next pick becomes list[n_sel] (a device array
+ * of at least cap global row indices, each in [0, N_global)).  Nothing depends on the host, so a run
+ * of prescribed picks replays from a CUDA graph; used to rebuild the state of a resumed checkpoint
+ * (replaces the chunked distance rebuild of cuda/multi/_shared.py:243-312 with the picks themselves,
+ * which reproduces h and voronoi bit for bit).
+ */
+CS_API int cs_force_pick_list(const cs_state* s, const int64_t* list, float val, cs_stream stream);
+
+/*
  * Resolve and commit pick number i = n_sel.  The winner is the largest key among the
  * world_size candidates (value first, then smallest global index: argmax_better,
  * kernels/_shared.cuh:24-27).  Writes selected[i], eps[i], X_sel[i], norms_sel[i]; the

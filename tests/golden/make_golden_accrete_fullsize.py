@@ -49,7 +49,8 @@ def main() -> None:
     ap.add_argument("--candidates", type=int, required=True)
     ap.add_argument("--max-k", type=int, required=True)
     ap.add_argument("--out", default=str(ROOT / "golden_out"))
-    ap.add_argument("--skip-reference", action="store_true")
+    ap.add_argument("--skip-reference", action="store_true", help="compare with the existing golden file instead")
+    ap.add_argument("--golden-dir", default="", help="where the existing golden file lies (default: --out)")
     ap.add_argument("--exchanges", default="nccl")
     a = ap.parse_args()
 
@@ -75,7 +76,7 @@ def main() -> None:
     gold_path = out / f"accrete_{a.anchors}_{a.candidates}_k{a.max_k}.npz"
 
     if a.skip_reference:
-        ref = np.load(gold_path)["selected"].astype(np.int64)
+        ref = np.load(Path(a.golden_dir or a.out) / gold_path.name)["selected"].astype(np.int64)
     else:
         from tests.golden.make_golden_gpu import load_reference
         coresets, _ = load_reference()

@@ -40,7 +40,9 @@ def main() -> None:
     ap.add_argument("--out", default=str(ROOT / "golden_out"))
     ap.add_argument("--exchanges", default="nccl,p2p", help="exchanges of this package to run beside the reference")
     ap.add_argument("--skip-reference", action="store_true",
-                    help="compare this package with an existing <out>/fullsize_<config>.npz instead of running the reference")
+                    help="compare this package with an existing fullsize_<config>.npz (in --golden-dir) instead of "
+                         "running the reference; a smaller --k compares a prefix")
+    ap.add_argument("--golden-dir", default="", help="where the existing golden file lies (default: --out)")
     a = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -71,8 +73,10 @@ def main() -> None:
                generate_s=round(t_gen, 2))
 
     if a.skip_reference:
-        z = np.load(gold_path)
-        ref_sel, ref_eps = z["selected"].astype(np.int64), z["eps"]
+        z = np.load(Path(a.golden_dir or a.out) / gold_path.name)
+        if int(z["rows"]) != w.n_rows:
+            raise SystemExit(f"{gold_path.name} is for {int(z['rows'])} rows, this run has {w.n_rows}")
+        ref_sel, ref_eps = z["selected"].astype(np.int64)[: w.k], z["eps"][: w.k]
     else:
         from tests.golden.make_golden_gpu import load_reference
         coresets, _ = load_reference()

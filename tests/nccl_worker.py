@@ -32,6 +32,9 @@ def main() -> None:
     if cfg.get("mode") == "accrete":
         failures = accrete_mode(cfg, rank, world, dev)
         cfg = dict(cfg, cases=[])
+    if cfg.get("mode") == "resume":
+        failures = resume_mode(cfg, rank, world, dev)
+        cfg = dict(cfg, cases=[])
     for case in cfg["cases"]:
         N, D, k, seed = case["N"], case["D"], case["k"], case.get("seed")
         X_np = with_duplicates(gaussian_mixture(N, D, 8, seed=N + D), 30, seed=2)
@@ -57,6 +60,51 @@ def main() -> None:
     out.write_text(json.dumps({"failures": failures}))
     dist.barrier()
     dist.destroy_process_group()
+
+
+def resume_mode(cfg, rank, world, dev):
+    """fps_sharded with checkpoints, then resume_from to a larger k (file names and cadence as
+    src/coresets/cuda/multi/fps_sharded.py:269-281, 422-446): ids and radii of the resumed run must
+    equal the uninterrupted run's and the oracle's, bit for bit."""
+    import oracle
+    from coresets_b200 import engine, fps_sharded
+    from tests.data import gaussian_mixture, with_duplicates
+    failures = []
+    out = Path(cfg["out_dir"])
+    N, D, k_ck, k_full, every = cfg["N"], cfg["D"], cfg["k_ck"], cfg["k_full"], cfg["every"]
+    X_np = with_duplicates(gaussian_mixture(N, D, 8, seed=N + D), 30, seed=2)
+    base = N // world
+    sizes = [base] * (world - 1) + [N - base * (world - 1)]
+    offs = [sum(sizes[:r]) for r in range(world)]
+    X_local = torch.from_numpy(np.ascontiguousarray(X_np[offs[rank] : offs[rank] + sizes[rank]])).to(dev)
+    prefix = str(out / "ck")
+    sel_a, eps_a = fps_sharded(X_local, k_ck, checkpoint_path=prefix, checkpoint_every=every, verbose=False)
+    dist.barrier()
+    if rank == 0:
+        steps = sorted(int(p.name.split("_k")[1].split("_")[0]) for p in out.glob("ck_k*_ids.npy"))
+        want = sorted(set(range(every, k_ck, every)) | {k_ck - 1})
+        if steps != want:
+            failures.append(f"checkpoint steps {steps} != {want}")
+        if (out / "ck_latest.txt").read_text() != f"{k_ck - 1}\n":
+            failures.append("latest.txt does not name the last pick")
+        ids = np.load(out / f"ck_k{k_ck - 1:010d}_ids.npy")
+        if ids.dtype != np.int64 or not np.array_equal(ids, sel_a.cpu().numpy()):
+            failures.append("final checkpoint ids differ from the returned picks")
+    dist.barrier()
+    sel_b, eps_b = fps_sharded(X_local, k_full, resume_from=prefix, verbose=False)
+    sel_c, eps_c = fps_sharded(X_local, k_full, verbose=False)
+    if not torch.equal(sel_b, sel_c):
+        failures.append(f"resumed picks differ from the uninterrupted run on rank {rank}")
+    if not np.array_equal(eps_b.numpy().view(np.int32), eps_c.numpy().view(np.int32)):
+        failures.append(f"resumed radii differ from the uninterrupted run on rank {rank}")
+    norms = np.concatenate([
+        engine.row_norms(torch.from_numpy(np.ascontiguousarray(X_np[offs[r] : offs[r] + sizes[r]])).to(dev)).cpu().numpy()
+        for r in range(world)])
+    o_sel, o_eps, _, _ = oracle.fps_sharded(X_np, norms, k_full, sizes, first=0)
+    if not np.array_equal(sel_b.cpu().numpy(), o_sel) or not np.array_equal(eps_b.numpy().view(np.int32), o_eps.view(np.int32)):
+        failures.append(f"resumed run differs from the oracle on rank {rank}")
+    dist.barrier()
+    return failures
 
 
 def accrete_mode(cfg, rank, world, dev):

@@ -98,3 +98,18 @@ def test_fps_sharded_cell_index_multi(tmp_path, world, xchg):
         pytest.skip(f"needs {world} GPUs")
     _launch(world, dict(cases=_cases(world), out_dir=str(tmp_path)),
             extra_env=dict(CELLS_EAGER, CORESETS_B200_EXCHANGE=xchg, CORESETS_B200_XCHG_TIMEOUT_MS="5000"))
+
+
+def test_fps_sharded_checkpoint_resume_world1(tmp_path):
+    """Checkpoint cadence, file names, and resume to a larger k through the graph-replayed forced
+    picks, on a one-rank NCCL group (runs on a single GPU)."""
+    _launch(1, dict(mode="resume", N=6000, D=64, k_ck=150, k_full=260, every=40, out_dir=str(tmp_path)))
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("xchg", ["nccl", "p2p"])
+def test_fps_sharded_checkpoint_resume_multi(tmp_path, world, xchg):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _launch(world, dict(mode="resume", N=6001, D=128, k_ck=150, k_full=260, every=40, out_dir=str(tmp_path)),
+            extra_env={"CORESETS_B200_EXCHANGE": xchg, "CORESETS_B200_XCHG_TIMEOUT_MS": "5000"})
