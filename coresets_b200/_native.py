@@ -16,6 +16,7 @@ from . import build as _build
 CS_ABI_VERSION = 7
 SELECT_SCRATCH_BYTES = 8192
 F_ELEMENT_ORDER = 1
+F_PDL = 2
 F_TEST_STALL_PIPE = 0x100
 CS_CTL_BYTES = 256
 CELL_TILE = 256

@@ -224,6 +224,7 @@ __device__ __forceinline__ bool cell_can_skip(const double dsl, const double h0,
 // step kernel rebuilds them) and seeds the next pick's arg-max key with the best key among the cells
 // that are NOT visited.
 __global__ void __launch_bounds__(1024) cells_select_kernel(const cs_state s, const cs_cells c, const double g) {
+    pdl_enter();
     __shared__ int s_cells[1024], s_chunks[1024];
     __shared__ u64 s_best[32];
     __shared__ u64 s_slots[32];
@@ -401,6 +402,7 @@ __device__ __forceinline__ void warp_keys_to_cells(u64* seg_key, const u64 key, 
 
 template <int CPL, bool FULL, bool HALF>
 __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) cells_scan_kernel(const cs_state s, const cs_cells cl) {
+    pdl_enter();
     __shared__ u64 s_keys[kWarps];
     __shared__ int s_cum[kCellWorkSmem], s_cell[kCellWorkSmem];
 
@@ -540,6 +542,7 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) cells_scan_kernel(con
 
 template <int CPL, bool FULL, bool HALF>
 __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) cells_eval_kernel(const cs_state s, const cs_cells cl) {
+    pdl_enter();
     __shared__ u64 s_keys[kWarps];
     __shared__ int s_last;
 

@@ -7,6 +7,7 @@ namespace {
 
 // ---- kernel A: resolve + commit + triangle bounds ------------------------------------------
 __global__ void __launch_bounds__(kThreads) commit_bound_kernel(const cs_state s, const unsigned rules) {
+    pdl_enter();
     extern __shared__ __align__(16) float s_cen[];
     Ctl* ctl = reinterpret_cast<Ctl*>(s.ctl);
     const int i = ctl->n_sel;

@@ -101,6 +101,15 @@ __device__ __forceinline__ float sq_dist(float n_row, float n_new, float dot) {
     return __fsub_rn(__fadd_rn(n_row, n_new), __fadd_rn(dot, dot));
 }
 
+// First statement of every kernel of the per-pick chain.  Under a programmatic dependent launch
+// the grid may already be resident while its predecessor runs: wait for the predecessor's
+// completion (and the visibility of its writes) before reading anything, then let the successor
+// become resident in turn.  Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ float4 ld_stream4(const float4* p) { return __ldcs(p); }
 
 // Generic warp dot: row in global memory, centre anywhere (shared or global); any D.

@@ -108,6 +108,30 @@ int tune_kernel(K kernel, KernelTune& t, const int dev, const size_t smem, const
     return CS_OK;
 }
 
+// Launch that may overlap its start with the tail of the kernel before it on the stream
+// (programmatic dependent launch): the grid is made resident early and its first instruction,
+// griddepcontrol.wait, holds it until the predecessor has completed and flushed its memory.  Taken
+// when the state carries CS_F_PDL; a plain launch otherwise (the wait is then a no-op).
+template <typename... KArgs, typename... Args>
+int launch_chain(const bool pdl, void (*kernel)(KArgs...), const int grid, const int block, const size_t smem,
+                 cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...) != cudaSuccess) {
+        g_last_cuda = cudaGetLastError();
+        return CS_E_LAUNCH;
+    }
+    return CS_OK;
+}
+
 int validate(const cs_state* s) {
     if (!s || !s->ctl || !s->X_sel || !s->norms_sel || !s->dSL_quarter) return CS_E_ARG;
     if (s->N_local < 0 || s->D <= 0 || s->cap <= 0 || s->world_size < 1 || s->shard_offset < 0) return CS_E_ARG;
@@ -164,8 +188,7 @@ int launch_step(const cs_state* s, unsigned mode, cudaStream_t st, const DevInfo
     int64_t want = (tiles + kWarps - 1) / kWarps;
     int64_t cap = (int64_t)sms * occ_blocks;     // persistent grid: a multiple of the SM count
     int grid = (int)(want < 1 ? 1 : (want < cap ? want : cap));
-    fps_step_kernel<CPL, FULL, HALF><<<grid, kThreads, smem, st>>>(*s, mode, n_bound);
-    return check_launch();
+    return launch_chain((s->flags & CS_F_PDL) != 0, fps_step_kernel<CPL, FULL, HALF>, grid, kThreads, smem, st, *s, mode, n_bound);
 }
 
 // prune mode with deferred rows (rows in whole 16-byte chunks, D <= 1024)
@@ -182,8 +205,7 @@ int launch_step_queue(const cs_state* s, cudaStream_t st, const DevInfo& dv) {
     int64_t want = (tiles + kWarps - 1) / kWarps;
     int64_t cap = (int64_t)sms * occ_blocks;     // persistent grid: a multiple of the SM count
     int grid = (int)(want < 1 ? 1 : (want < cap ? want : cap));
-    fps_step_queue_kernel<CPL, FULL, HALF><<<grid, kThreads, smem, st>>>(*s, n_bound);
-    return check_launch();
+    return launch_chain((s->flags & CS_F_PDL) != 0, fps_step_queue_kernel<CPL, FULL, HALF>, grid, kThreads, smem, st, *s, n_bound);
 }
 
 template <int L, int CPL>
@@ -305,8 +327,7 @@ int cs_commit_bound(const cs_state* s, uint32_t rules, cs_stream stream) {
     int64_t want = (s->cap + kWarps - 1) / kWarps;
     int64_t lim = (int64_t)d.sms * 2;
     int grid = (int)(want < 1 ? 1 : (want < lim ? want : lim));
-    commit_bound_kernel<<<grid, kThreads, smem, (cudaStream_t)stream>>>(*s, rules);
-    return check_launch();
+    return launch_chain((s->flags & CS_F_PDL) != 0, commit_bound_kernel, grid, kThreads, smem, (cudaStream_t)stream, *s, rules);
 }
 
 int cs_fps_step(const cs_state* s, uint32_t mode, cs_stream stream) {
@@ -494,12 +515,11 @@ int launch_step_cells(const cs_state* s, const cs_cells* c, cudaStream_t st, con
     // persistent grids: the numbers of tiles and of queued rows are only known on the device
     const int64_t tiles = (s->N_local + kCellTile - 1) / kCellTile + 1;
     const int64_t want_scan = (tiles + kWarps - 1) / kWarps, cap_scan = (int64_t)dv.sms * per_scan;
-    cells_scan_kernel<CPL, FULL, HALF><<<(int)(want_scan < cap_scan ? want_scan : cap_scan), kThreads, 0, st>>>(*s, *c);
-    rc = check_launch();
+    const bool pdl = (s->flags & CS_F_PDL) != 0;
+    rc = launch_chain(pdl, cells_scan_kernel<CPL, FULL, HALF>, (int)(want_scan < cap_scan ? want_scan : cap_scan), kThreads, 0, st, *s, *c);
     if (rc) return rc;
     const int64_t want_eval = ((int64_t)c->q_cap + kThreads - 1) / kThreads, cap_eval = (int64_t)dv.sms * per_eval;
-    cells_eval_kernel<CPL, FULL, HALF><<<(int)(want_eval < cap_eval ? want_eval : cap_eval), kThreads, 0, st>>>(*s, *c);
-    return check_launch();
+    return launch_chain(pdl, cells_eval_kernel<CPL, FULL, HALF>, (int)(want_eval < cap_eval ? want_eval : cap_eval), kThreads, 0, st, *s, *c);
 }
 
 }  // namespace
@@ -554,8 +574,7 @@ int cs_cells_select(const cs_state* s, const cs_cells* c, cs_stream stream) {
     // norms: D products and sums in the dot product, D in each norm, a few more in the final formula;
     // the factor 4 is slack
     const double g = 4.0 * ((double)s->D + 32.0) * 5.9604644775390625e-8;
-    cells_select_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(*s, *c, g);
-    return check_launch();
+    return launch_chain((s->flags & CS_F_PDL) != 0, cells_select_kernel, 1, 1024, 0, (cudaStream_t)stream, *s, *c, g);
 }
 
 int cs_fps_step_cells(const cs_state* s, const cs_cells* c, cs_stream stream) {

@@ -91,6 +91,7 @@ __device__ __forceinline__ void tile_rows(const float4* __restrict__ X4, const i
 template <int CPL, bool FULL, bool HALF>
 __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const cs_state s, const unsigned mode,
                                                                            const int n_bound_smem) {
+    pdl_enter();
     // dynamic shared memory: the first n_bound_smem triangle bounds (the per-row bound lookup is
     // then a shared-memory read instead of an L2 round trip), then the centre on the generic path
     extern __shared__ __align__(16) float s_dyn[];

@@ -27,6 +27,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 template <int CPL, bool FULL, bool HALF>
 __global__ void __launch_bounds__(kThreads, CPL == 0 ? 2 : CS_MIN_BLOCKS) fps_step_queue_kernel(const cs_state s, const int n_bound_smem) {
+    pdl_enter();
     static_assert(kRowsPerLane == 4, "the deferred-row kernel reads four rows per lane");
     // dynamic shared memory: the scan ring (per warp and slot 128 h, then 128 voronoi words), the
     // first n_bound_smem triangle bounds, then (CPL == 0, the path for any row width and for the

@@ -61,6 +61,10 @@ extern "C" {
                               ... with one fma each) even when D % 4 == 0: the order the reference uses
                               for float16 / float64 inputs (_shared.cuh:55-58), whose rows the caller
                               passes converted to float32 */
+#define CS_F_PDL 2u          /* launch the kernels of a pick (commit, cell selection, scan, evaluation, the
+                              prune-mode step) as programmatic dependents of the kernel before them on the
+                              stream: their start overlaps the predecessor's tail, they read nothing
+                              before it has completed */
 #define CS_F_TEST_STALL_PIPE 0x100u /* test hook: the dense kernel's producer starts no copy, so that the
                               consumers' bounded wait runs out (status 4) without any fault */
 /* cs_commit_bound flags */

@@ -55,6 +55,7 @@ def build(reference_root: str) -> Path:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("CORESETS_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("CORESETS_REFERENCE_ROOT"),
+                    required=not os.environ.get("CORESETS_REFERENCE_ROOT"), help="the reference checkout (or set CORESETS_REFERENCE_ROOT)")
     a = ap.parse_args()
     print(build(a.reference))

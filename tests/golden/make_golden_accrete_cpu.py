@@ -109,7 +109,8 @@ def worker(ref_root: str, out_dir: str):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("CORESETS_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("CORESETS_REFERENCE_ROOT"),
+                    required=not os.environ.get("CORESETS_REFERENCE_ROOT"), help="the reference checkout (or set CORESETS_REFERENCE_ROOT)")
     ap.add_argument("--worker-out", default=None)
     a = ap.parse_args()
     if a.worker_out:

@@ -30,7 +30,8 @@ KNOB_SETS = {"plain": {}, "knobs": {"CORESETS_BISECT_SEED": "1", "CORESETS_FILL_
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("CORESETS_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("CORESETS_REFERENCE_ROOT"),
+                    required=not os.environ.get("CORESETS_REFERENCE_ROOT"), help="the reference checkout (or set CORESETS_REFERENCE_ROOT)")
     a = ap.parse_args()
     import torch.distributed as dist
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")

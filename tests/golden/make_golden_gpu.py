@@ -2,7 +2,7 @@
 
 Needs (all git-ignored, produced on a machine that has the reference checkout):
   oracle/_ref/site/   `pip install --no-deps --target oracle/_ref/site <reference checkout>`
-  oracle/_ref/build/  `python oracle/build_ref.py` (the reference's kernels, its own flags)
+  oracle/_ref/build/  `python oracle/build_ref.py --reference <reference checkout>` (the reference's kernels, its own flags)
 
 Run on a B200:   python tests/golden/make_golden_gpu.py --out <output directory>
 then copy the produced *.npz next to this file.  Each file holds the inputs that cannot be

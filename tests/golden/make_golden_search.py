@@ -19,7 +19,8 @@ from pathlib import Path
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("CORESETS_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("CORESETS_REFERENCE_ROOT"),
+                    required=not os.environ.get("CORESETS_REFERENCE_ROOT"), help="the reference checkout (or set CORESETS_REFERENCE_ROOT)")
     a = ap.parse_args()
     sys.path.insert(0, str(Path(a.reference) / "src"))
     from coresets.cuda.multi._base import MultiGPUAccrete

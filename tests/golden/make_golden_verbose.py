@@ -53,7 +53,8 @@ def mask(text: str) -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("CORESETS_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("CORESETS_REFERENCE_ROOT"),
+                    required=not os.environ.get("CORESETS_REFERENCE_ROOT"), help="the reference checkout (or set CORESETS_REFERENCE_ROOT)")
     a = ap.parse_args()
     import torch.distributed as dist
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")

@@ -76,3 +76,13 @@ def test_float16_gross_violation_is_reported_like_the_reference():
     assert "accrete: sep > cov violated at level k=9 (size=512)" in msg
     assert "sep=5.66210904e-01, cov=5.69710191e-01, rel_gap=-1.225e-02" in msg
     assert msg.endswith("Gross violation, not float noise.")
+
+
+def test_accrete_sharded_fused_lanes_match_reference(tmp_path):
+    """The one-pass-over-X lanes kernel on the real driver: dense mode routes cs_fps_step_lanes to
+    fps_step_lanes_kernel, CORESETS_LANES_MIN_STEPS=1 makes every seeded walk start with lanes; the
+    lists must be the ones the reference's accrete_sharded wrote (default knobs and
+    CORESETS_BISECT_SEED=1 CORESETS_FILL_CHUNK=256)."""
+    from tests.test_gpu_multi import _launch
+    _launch(1, dict(mode="accrete", cases=[], out_dir=str(tmp_path)), timeout=1500,
+            extra_env={"CORESETS_B200_MODE": "dense", "CORESETS_LANES_MIN_STEPS": "1"})

@@ -51,12 +51,3 @@ def test_decode_key_round_trip():
     # a key read back as a signed 64-bit integer decodes the same
     k = make_key(np.float32(5.0), 77)
     assert _native.decode_key(k - (1 << 64)) == (5.0, 77)
-
-
-def test_integration_notes_mirror_the_state_struct():
-    """The binding sketch shown to reference maintainers lists cs_state's fields in order."""
-    text = (ROOT / "INTEGRATION.md").read_text()
-    block = text[text.index("class CsState(ctypes.Structure)"):text.index("_lib = ctypes.CDLL")]
-    names = re.findall(r'\("(\w+)",\s*ctypes\.', block)
-    assert names == [f[0] for f in _native.CsState._fields_]
-    assert f"cs_version() == {_native.CS_ABI_VERSION}" in text
