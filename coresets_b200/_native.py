@@ -178,7 +178,7 @@ class Native:
             ("cs_init_state", [sp, vp]),
             ("cs_reset_ctl", [sp, ctypes.c_int32, vp]),
             ("cs_force_pick", [sp, ctypes.c_int64, ctypes.c_float, vp]),
-            ("cs_force_pick_list", [sp, vp, ctypes.c_float, vp]),
+            ("cs_force_pick_list", [sp, vp, vp, ctypes.c_float, vp]),
             ("cs_commit_bound", [sp, ctypes.c_uint32, vp]),
             ("cs_fps_step", [sp, ctypes.c_uint32, vp]),
             ("cs_sim_begin", [sp, ctypes.c_float, vp]),
@@ -225,8 +225,8 @@ class Native:
     def force_pick(self, s: CsState, global_idx: int, val: float, stream: int) -> None:
         self._check(self.lib.cs_force_pick(ctypes.byref(s), global_idx, val, stream), "cs_force_pick")
 
-    def force_pick_list(self, s: CsState, list_ptr: int, val: float, stream: int) -> None:
-        self._check(self.lib.cs_force_pick_list(ctypes.byref(s), list_ptr, val, stream), "cs_force_pick_list")
+    def force_pick_list(self, s: CsState, list_ptr: int, vals_ptr, val: float, stream: int) -> None:
+        self._check(self.lib.cs_force_pick_list(ctypes.byref(s), list_ptr, vals_ptr, val, stream), "cs_force_pick_list")
 
     def commit_bound(self, s: CsState, rules: int, stream: int) -> None:
         self._check(self.lib.cs_commit_bound(ctypes.byref(s), rules, stream), "cs_commit_bound")

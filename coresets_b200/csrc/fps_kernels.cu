@@ -301,11 +301,11 @@ int cs_force_pick(const cs_state* s, int64_t global_idx, float val, cs_stream st
     return check_launch();
 }
 
-int cs_force_pick_list(const cs_state* s, const int64_t* list, float val, cs_stream stream) {
+int cs_force_pick_list(const cs_state* s, const int64_t* list, const float* vals, float val, cs_stream stream) {
     int rc = validate(s);
     if (rc) return rc;
     if (!list) return CS_E_ARG;
-    force_pick_list_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(*s, list, val);
+    force_pick_list_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(*s, list, vals, val);
     return check_launch();
 }
 
@@ -687,12 +687,19 @@ extern "C" int cs_fps_step_noalloc(const float* X, const float* norms, float* h,
     s.shard_offset = shard_offset;
     s.D = D;
     s.world_size = 1;
+    // (the two bases below are formed by integer arithmetic on DEVICE addresses and point outside the
+    // scratch object; the kernel only ever dereferences slot sel_pos, which lies inside it)
     const uintptr_t row_slot = (uintptr_t)(scratch + CS_CTL_BYTES + 256);
     const uintptr_t norm_slot = (uintptr_t)(scratch + CS_CTL_BYTES);
     s.X_sel = reinterpret_cast<float*>(row_slot - (uintptr_t)sel_pos * (uintptr_t)D * sizeof(float));
     s.norms_sel = reinterpret_cast<float*>(norm_slot - (uintptr_t)sel_pos * sizeof(float));
     s.dSL_quarter = const_cast<float*>(dSL_quarter ? dSL_quarter : reinterpret_cast<const float*>(norm_slot));
-    s.cap = (int64_t)sel_pos + 1;
+    // capacity = the next power of two above the pick position: the step kernel sizes its staged
+    // bound table (and with it its shared memory and grid) from the capacity, so the launch shape
+    // changes O(log k) times over a run instead of with every pick (it reads only sel_pos bounds)
+    int64_t cap_q = 1;
+    while (cap_q < (int64_t)sel_pos + 1) cap_q <<= 1;
+    s.cap = cap_q;
     s.selected = nullptr;
     s.eps = nullptr;
     s.ctl = scratch;

@@ -41,11 +41,12 @@ __global__ void force_pick_kernel(const cs_state s, const int64_t gidx, const fl
 
 // The same with the row taken from a device list at the position of the pick counter, so that a
 // run of prescribed picks (a resumed checkpoint) can be replayed from a CUDA graph.
-__global__ void force_pick_list_kernel(const cs_state s, const int64_t* __restrict__ list, const float val) {
+__global__ void force_pick_list_kernel(const cs_state s, const int64_t* __restrict__ list,
+                                       const float* __restrict__ vals, const float val) {
     const Ctl* ctl = reinterpret_cast<const Ctl*>(s.ctl);
     const int i = ctl->n_sel;
     if (i >= s.cap) return;                                // the commit kernel reports the overflow
-    force_pick_body(s, list[i], val);
+    force_pick_body(s, list[i], vals ? vals[i] : val);
 }
 
 __global__ void sim_begin_kernel(Ctl* ctl, float sep) {

@@ -430,7 +430,11 @@ class AccreteDriver:
                 sel_pos = self._record(idx)
                 self.sep = step_seps[j + 1]
                 self.trace("replay", sel_pos, idx, self.sep, self.sep)
-                self._commit_known(idx, self.sep)
+            # the kept picks go back in as one run of prescribed picks (replayed from CUDA graphs on
+            # the device) instead of one forced pick at a time
+            if best_m > 0:
+                self.E.run_forced(added[:best_m], values=step_seps[1 : best_m + 1])
+                self._key_valid = True
         return budget - best_m
 
     # ------------------------------------------------------------------ bisect, single-GPU flavour

@@ -302,7 +302,8 @@ class ShardEngine:
         if how == "forced":
             if self.world_size > 1 and self.xchg == XCHG_PEER:
                 self.native.xchg_wait(self.state, self._stream())     # see _before_publish
-            self.native.force_pick_list(self.state, self._forced_list.data_ptr(), float("inf"), self._stream())
+            self.native.force_pick_list(self.state, self._forced_list.data_ptr(), self._forced_vals.data_ptr(),
+                                        float("inf"), self._stream())
             how = None
         self.exchange()
         self.commit(rules)
@@ -321,7 +322,7 @@ class ShardEngine:
         self.force_pick(global_idx, val)
         self._pick_body(rules)
 
-    def run_forced(self, indices, rules: int = RULE_NONE) -> None:
+    def run_forced(self, indices, rules: int = RULE_NONE, values=None) -> None:
         """Commit the prescribed global rows ``indices`` one after the other as the next centres, each
         with its update -- ``pick_forced`` for a whole list.  On the device the rows are read from a
         list indexed by the pick counter, so the run replays from CUDA graphs like free picks
@@ -329,15 +330,19 @@ class ShardEngine:
         idx = [int(v) for v in (indices.tolist() if hasattr(indices, "tolist") else indices)]
         if not idx:
             return
-        if not (self.on_cuda and _graphs_enabled() and self.n_host is not None):
-            for g in idx:
-                self.pick_forced(g, rules=rules)
+        vals = [float("inf")] * len(idx) if values is None else [float(v) for v in values]
+        if not (self.on_cuda and _graphs_enabled() and self.n_host is not None) or len(idx) < 4:
+            for g, v in zip(idx, vals):
+                self.pick_forced(g, v, rules=rules)
             return
         if self.n_host + len(idx) > self.cap:
             raise ValueError(f"{len(idx)} forced picks after {self.n_host} exceed the capacity {self.cap}")
         if not hasattr(self, "_forced_list"):
             self._forced_list = torch.zeros(self.cap, dtype=torch.int64, device=self.device)
-        self._forced_list[self.n_host : self.n_host + len(idx)] = torch.tensor(idx, dtype=torch.int64).to(self.device)
+            self._forced_vals = torch.zeros(self.cap, dtype=torch.float32, device=self.device)
+        lo, hi = self.n_host, self.n_host + len(idx)
+        self._forced_list[lo:hi] = torch.tensor(idx, dtype=torch.int64).to(self.device)
+        self._forced_vals[lo:hi] = torch.tensor(vals, dtype=torch.float32).to(self.device)
         self._replay(len(idx), rules, "forced")
 
     def _graph(self, n: int, rules: int, how=None):

@@ -168,12 +168,13 @@ CS_API int cs_force_pick(const cs_state* s, int64_t global_idx, float val, cs_st
 
 /*
  * cs_force_pick with the row read on the device: the next pick becomes list[n_sel] (a device array
- * of at least cap global row indices, each in [0, N_global)).  Nothing depends on the host, so a run
+ * of at least cap global row indices, each in [0, N_global)) with value vals[n_sel], or `val` when
+ * vals is NULL.  Nothing depends on the host, so a run
  * of prescribed picks replays from a CUDA graph; used to rebuild the state of a resumed checkpoint
  * (replaces the chunked distance rebuild of cuda/multi/_shared.py:243-312 with the picks themselves,
  * which reproduces h and voronoi bit for bit).
  */
-CS_API int cs_force_pick_list(const cs_state* s, const int64_t* list, float val, cs_stream stream);
+CS_API int cs_force_pick_list(const cs_state* s, const int64_t* list, const float* vals, float val, cs_stream stream);
 
 /*
  * Resolve and commit pick number i = n_sel.  The winner is the largest key among the
@@ -346,7 +347,9 @@ CS_API int cs_fps_step_cells(const cs_state* s, const cs_cells* c, cs_stream str
  * Inputs: X, norms, h, voronoi as in cs_state; `centre` = the D floats of the new centre,
  * `norm_new` its squared norm, `sel_pos` its position in the selection (written into voronoi;
  * 0 selects the dense first-centre update), `dSL_quarter` = sel_pos triangle bounds (may be NULL
- * when sel_pos == 0).  Outputs: h / voronoi updated in place; *out_key = the arg-max key of the
+ * when sel_pos == 0).  Precondition: the centre's own row already carries h = -1 (what
+ * cs_commit_bound does for the row it commits); the step never selects, it only updates.
+ * Outputs: h / voronoi updated in place; *out_key = the arg-max key of the
  * next pick (value-orderable bits << 32 | 0xFFFFFFFF - global index, 0 = no candidate);
  * *out_live_rows (optional) = rows whose distance was evaluated.  All pointers are device
  * pointers.  D above CS_NOALLOC_MAX_D returns CS_E_SCRATCH.

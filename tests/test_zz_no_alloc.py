@@ -22,7 +22,8 @@ def _stream(dev):
     return torch.cuda.current_stream(dev).cuda_stream
 
 
-@pytest.mark.parametrize("N,D,mode", [(5000, 128, MODE_PRUNE), (3001, 64, MODE_DENSE), (2000, 50, MODE_PRUNE)])
+@pytest.mark.parametrize("N,D,mode", [(5000, 128, MODE_PRUNE), (3001, 64, MODE_DENSE), (2000, 50, MODE_PRUNE),
+                                      (1500, 2048, MODE_PRUNE), (2000, 50, MODE_DENSE)])
 def test_noalloc_step_matches_regular_step_twice_in_a_row(N, D, mode):
     dev = torch.device("cuda:0")
     native = _native.get_native()
