@@ -426,8 +426,9 @@ def run_ours(args):
         if world == 1 and n_local > SHARD_ROWS:
             # the shard the reference's own CUDA path can take on one GPU (see --impl reference, `cuda`)
             Xs, ns = X[:SHARD_ROWS], norms[:SHARD_ROWS]
-            shard, _ = prune_leg(Xs, ns, pcap, 0, 1, 1 + args.prune_picks, K, device, cells=True)
+            shard, sheng = prune_leg(Xs, ns, pcap, 0, 1, 1 + args.prune_picks, K, device, cells=True)
             shard["what"] = f"product mode on the first {SHARD_ROWS} rows of {w.name}, row 0 first (one GPU)"
+            sheng = Xs = ns = None
             torch.cuda.empty_cache()
     parity["equal"] = (None if any(p["equal"] is None for p in parity.values())
                        else all(p["equal"] for p in parity.values()))
@@ -651,11 +652,12 @@ def run_config(name, args, world, rank, device, K, W):
     sizes, offsets = compute_shard_layout(w.n_rows, world)
     n_local, off = sizes[rank], offsets[rank]
     free_b, _ = torch.cuda.mem_get_info(device)
-    ok = torch.tensor([1 if n_local * (w.dim * 4 + 28) + (2 << 30) < free_b else 0], device=device)
+    ok = torch.tensor([1 if n_local * (w.dim * 4 + 12) + (1 << 30) < free_b else 0], device=device)
     if world > 1:
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if int(ok.item()) == 0:
-        return {"skipped": f"{n_local * w.dim * 4 / 1e9:.1f} GB of rows per GPU do not fit beside the state"}
+        return {"skipped": f"{n_local * w.dim * 4 / 1e9:.1f} GB of rows per GPU do not fit beside the state "
+                           f"({free_b / 1e9:.1f} GB free)"}
     X = torch.empty((n_local, w.dim), dtype=torch.float32, device=device)
     MixtureSource(w).fill(X, off)
     norms = engine.row_norms(X)

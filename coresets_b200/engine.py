@@ -230,7 +230,7 @@ class ShardEngine:
             s.peer_win[r] = ptr
         s.xchg_timeout_ms = int(os.environ.get("CORESETS_B200_XCHG_TIMEOUT_MS", "10000"))
         s.flags = ((_native.F_ELEMENT_ORDER if self.element_order else 0) | self._extra_flags
-                   | (_native.F_PDL if self.on_cuda and _knob("PDL", 0) else 0))
+                   | (_native.F_PDL if self.on_cuda and _knob("PDL", 1) else 0))
         return s
 
     def rebind(self, *, h: Optional[torch.Tensor] = None, voronoi: Optional[torch.Tensor] = None) -> None:
