@@ -77,9 +77,15 @@ def accrete_mode(cfg, rank, world) -> None:
                 kw.update(resume_from=str(out / case["resume"]))
             if case.get("trace"):
                 kw.update(trace_path=str(out / f"{case['name']}_trace_{rank}.tsv"))
-            res = sh.accrete_voronoi_multi_sharded(
-                Xl, rank, world, case["n_anchor"], X.shape[0], sizes, torch.from_numpy(order),
-                max_k=case["max_k"], n_target=case.get("n_target"), verbose=False, **kw)
+            if case.get("replicated"):      # every rank holds the whole matrix (accrete_voronoi_multi)
+                from coresets_b200.cuda.multi import accrete_voronoi_multi
+                na = case["n_anchor"]
+                res = accrete_voronoi_multi(torch.from_numpy(X[:na]), torch.from_numpy(X[na:]), torch.from_numpy(order),
+                                            rank, world, max_k=case["max_k"], verbose=False)
+            else:
+                res = sh.accrete_voronoi_multi_sharded(
+                    Xl, rank, world, case["n_anchor"], X.shape[0], sizes, torch.from_numpy(order),
+                    max_k=case["max_k"], n_target=case.get("n_target"), verbose=False, **kw)
             assert res.dtype == torch.int64
             np.save(out / f"{case['name']}_{rank}.npy", res.numpy())
     finally:

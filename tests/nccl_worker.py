@@ -131,6 +131,17 @@ def accrete_mode(cfg, rank, world, dev):
                 failures.append(f"{name}/{tag}: {nd} ids differ from the reference on rank {rank} (world {world})")
         for k in ("CORESETS_BISECT_SEED", "CORESETS_FILL_CHUNK"):
             os.environ.pop(k, None)
+        if Xl.dtype == torch.float32:
+            # the replicated entry (whole matrix on every rank) against the reference's replicated driver
+            # (tests/golden/acc_replicated.npz), or its sharded list where that file has no such case
+            rep = golden / "acc_replicated.npz"
+            want = np.load(rep)[name] if rep.is_file() and name in np.load(rep).files else z["sharded_plain"]
+            Xf = torch.from_numpy(X_np).to(dev)
+            na = c["n_anchor"]
+            res = coresets_b200.cuda.multi.accrete_voronoi_multi(Xf[:na], Xf[na:], order, rank, world, max_k=c["max_k"],
+                                                                 verbose=False)
+            if not np.array_equal(res.cpu().numpy(), want):
+                failures.append(f"{name}/replicated: ids differ from the reference on rank {rank} (world {world})")
         dist.barrier()
     return failures
 

@@ -66,6 +66,10 @@ def test_sharded_driver_matches_reference(tmp_path, world):
         cases.append(dict(base, name=f"{name}_deep", env={"CORESETS_BISECT_SEED": "1", "CORESETS_BISECT_GALLOP_DEEP": "1",
                                                          "CORESETS_FILL_CHUNK": "64"}))
         cases.append(dict(base, name=f"{name}_nolazy", env={"CORESETS_BISECT_SEED": "1", "CORESETS_LAZY_FORWARD": "0"}))
+        if "n_target" not in c:
+            # the replicated entry (whole matrix on every rank): the reference's three drivers give one list
+            # (its tests/test_determinism.py), so the sharded driver's golden list applies
+            cases.append(dict(base, name=f"{name}_repl", replicated=True))
     _run(world, dict(mode="accrete", cases=cases, out_dir=str(tmp_path)), timeout=900)
     for name in CASES:
         z = np.load(GOLDEN / f"accrete_cpu_{name}.npz")
@@ -75,6 +79,8 @@ def test_sharded_driver_matches_reference(tmp_path, world):
             np.testing.assert_array_equal(np.load(tmp_path / f"{name}_lanes_{r}.npy"), z[f"sharded_w{world}_knobs"])
             np.testing.assert_array_equal(np.load(tmp_path / f"{name}_deep_{r}.npy"), z[f"sharded_w{world}_deep"])
             np.testing.assert_array_equal(np.load(tmp_path / f"{name}_nolazy_{r}.npy"), z[f"sharded_w{world}_nolazy"])
+            if "n_target" not in CASES[name]:
+                np.testing.assert_array_equal(np.load(tmp_path / f"{name}_repl_{r}.npy"), z[f"sharded_w{world}"])
 
 
 def test_accrete_validation(fake_native):
