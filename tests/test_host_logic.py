@@ -116,3 +116,19 @@ def test_torch_backend_fps_reproduces_the_reference_python_fps():
     assert eps[0] == 0.0 and "fps" in coresets_b200.__all__
     seeded = coresets_b200.fps(X[:500], 5, torch.tensor([7, 3]))
     assert seeded[0][:2].tolist() == [7, 3] and float(seeded[1][0]) == 0.0 and float(seeded[1][1]) > 0.0
+
+
+def test_torch_backend_voronoi_fps_equals_fps():
+    """The triangle-bound variant picks what the dense one picks (the reference's own claim for its
+    two torch functions), sparse and dense branches both taken."""
+    import torch
+    from coresets_b200.pytorch import fps, voronoi_fps
+    from tests.data import gaussian_mixture
+    X = torch.from_numpy(gaussian_mixture(4000, 16, 8, seed=5))
+    a = fps(X, 200)
+    for frac in (0.5, 0.0):
+        b = voronoi_fps(X, 200, full_fraction=frac)
+        assert torch.equal(a[0], b[0]) and torch.equal(a[3], b[3])
+        assert torch.allclose(a[1], b[1], rtol=1e-5, atol=1e-5) and torch.allclose(a[2], b[2], rtol=1e-4, atol=1e-4)
+    s = voronoi_fps(X, 50, torch.tensor([9, 4]))
+    assert s[0][:2].tolist() == [9, 4] and torch.equal(s[0], fps(X, 50, torch.tensor([9, 4]))[0])
