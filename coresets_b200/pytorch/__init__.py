@@ -1,6 +1,7 @@
 """The reference's plain-torch backend (src/coresets/pytorch/): runs wherever ``X`` lives, one dense
 matrix-vector product per pick.  Not the accelerated path -- ``fps_cuda`` / ``fps_sharded`` never
 come through here -- but part of the package's public names (``coresets.fps``)."""
+from .accrete import accrete
 from .fps import fps, fps_update, voronoi_fps
 
-__all__ = ["fps", "fps_update", "voronoi_fps"]
+__all__ = ["accrete", "fps", "fps_update", "voronoi_fps"]

@@ -132,3 +132,24 @@ def test_torch_backend_voronoi_fps_equals_fps():
         assert torch.allclose(a[1], b[1], rtol=1e-5, atol=1e-5) and torch.allclose(a[2], b[2], rtol=1e-4, atol=1e-4)
     s = voronoi_fps(X, 50, torch.tensor([9, 4]))
     assert s[0][:2].tolist() == [9, 4] and torch.equal(s[0], fps(X, 50, torch.tensor([9, 4]))[0])
+
+
+def test_torch_backend_accrete_reproduces_the_reference():
+    """``coresets_b200.pytorch.accrete`` against the lists (and the printed table) the reference's own
+    plain-torch ``accrete`` produced (tests/golden/torch_accrete.npz, make_golden_torch_accrete.py)."""
+    import contextlib
+    import io
+    from pathlib import Path
+    import numpy as np
+    import torch
+    from coresets_b200.pytorch import accrete
+    from tests.golden.make_golden_torch_accrete import CASES, case_inputs
+    z = np.load(Path(__file__).resolve().parent / "golden" / "torch_accrete.npz")
+    torch.set_num_threads(1)
+    for name, c in CASES.items():
+        Xa, Xc, order = case_inputs(c)
+        buf = io.StringIO()
+        with contextlib.redirect_stdout(buf):
+            out = accrete(Xa, Xc, order, torch.arange(Xc.shape[0]), max_k=c["max_k"], verbose=True)
+        np.testing.assert_array_equal(out.numpy(), z[name])
+        assert buf.getvalue() == str(z[name + "_table"])
