@@ -78,7 +78,14 @@ class AccreteDriver:
         self.X_src = X_src
         kw = dict(shard_offset=layout.shard_offset, world_size=world, element_order=X_src is not None)
         self.E = _engine.ShardEngine(X_local, norms_local, self.max_sel, **kw)
-        self.S = _engine.ShardEngine(X_local, norms_local, self.max_sel, record=False, **kw)
+        # Probes can run through the cell index (built per probe from the reconstructed state) on shards
+        # of at least CORESETS_B200_CELLS_SIM_MIN_ROWS rows.  Off unless that knob is set: at 25 M rows
+        # per GPU it shortens the probes' steps by a quarter but a run by 6 % only, because three quarters
+        # of a large run go into the reconstruct step, whose arithmetic is the reference's.
+        self._sim_cells = (X_local.is_cuda and int(X_local.shape[0]) >= _env_int("CORESETS_B200_CELLS_SIM_MIN_ROWS", 1 << 40))
+        self._sim_cells_min_steps = _env_int("CORESETS_B200_CELLS_SIM_MIN_STEPS", 256)
+        self.S = _engine.ShardEngine(X_local, norms_local, self.max_sel, record=False, cells=self._sim_cells,
+                                     cells_any_rules=True, **kw)
         self.E.init_state()
         n_alloc = self.E.h.shape[0]
         mk = lambda dt: torch.empty(n_alloc, dtype=dt, device=self.device)  # noqa: E731
@@ -237,7 +244,8 @@ class AccreteDriver:
             if mine.numel() > 0:
                 h_mid[mine] = -1.0
 
-    def _sim_start(self, S, sep_mid: float, n_init: int) -> None:
+    def _sim_start(self, S, sep_mid: float, n_init: int, points_left: int = 0) -> None:
+        S.cells_hold = points_left < self._sim_cells_min_steps      # an index does not pay for a short probe
         if n_init > 0:
             S.X_sel[:n_init].copy_(self.E.X_sel[:n_init])
             S.norms_sel[:n_init].copy_(self.E.norms_sel[:n_init])
@@ -261,7 +269,7 @@ class AccreteDriver:
         """One bisect probe on the simulation engine's state: up to ``points_left`` unrestricted
         picks, viable as soon as the running separation beats the coverage
         (simulate.cu:10-90, multi.cu:428-528)."""
-        self._sim_start(self.S, sep_mid, n_init)
+        self._sim_start(self.S, sep_mid, n_init, points_left)
         return self._sim_finish(self.S, 0, points_left)
 
     def _lane_engines(self, n: int):
@@ -270,13 +278,14 @@ class AccreteDriver:
         if not hasattr(self, "_lanes"):
             self._lanes = [self.S]
         budget = float(os.environ.get("CORESETS_LANES_MEM_GB", "8")) * (1 << 30)
-        per_lane = max(self.layout.sizes) * 8 + self.max_sel * (self.dim * 4 + 12)
+        per_lane = max(self.layout.sizes) * (26 if self._sim_cells else 8) + self.max_sel * (self.dim * 4 + 12)
         n = max(1, min(n, 1 + int(budget // max(per_lane, 1))))
         world = self.layout.world_size if self.multi else 1
         while len(self._lanes) < n:
             self._lanes.append(_engine.ShardEngine(self.E.X, self.E.norms, self.max_sel, record=False,
                                                    shard_offset=self.layout.shard_offset, world_size=world,
-                                                   element_order=self.E.element_order))
+                                                   element_order=self.E.element_order, cells=self._sim_cells,
+                                                   cells_any_rules=True))
         return self._lanes[:n]
 
     def _simulate_lanes(self, engines, probes) -> List[bool]:
@@ -285,7 +294,7 @@ class AccreteDriver:
         each verdict is the lone probe's verdict."""
         W = len(probes)
         for S, p in zip(engines, probes):
-            self._sim_start(S, float(p["sep"]), p["n_init"])
+            self._sim_start(S, float(p["sep"]), p["n_init"], p["points_left"])
         left = [p["points_left"] for p in probes]
         verdict: List[Optional[bool]] = [None] * W
         active = list(range(W))

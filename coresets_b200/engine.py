@@ -122,7 +122,8 @@ class ShardEngine:
     def __init__(self, X_local: torch.Tensor, norms: torch.Tensor, cap: int, *, shard_offset: int = 0,
                  world_size: int = 1, group=None, mode: Optional[int] = None,
                  h: Optional[torch.Tensor] = None, voronoi: Optional[torch.Tensor] = None,
-                 record: bool = True, element_order: bool = False, cells: bool = False):
+                 record: bool = True, element_order: bool = False, cells: bool = False,
+                 cells_any_rules: bool = False):
         if X_local.dim() != 2:
             raise ValueError(f"X_local must be 2-D, got shape {tuple(X_local.shape)}")
         if X_local.dtype != torch.float32:
@@ -182,6 +183,8 @@ class ShardEngine:
             and self.D % 4 == 0 and self.D <= 1024 and self.cap <= 65536
             and self.N_local >= _knob("CELLS_MIN_ROWS", _CELLS_MIN_ROWS)
             and self.N_local + self.cap * _native.CELL_TILE < 2 ** 31)
+        self.cells_any_rules = bool(cells_any_rules)   # also for picks with simulation rules (accretion probes)
+        self.cells_hold = False                # the caller's veto for the run in hand (e.g. a short probe)
         self._cells: Optional[CsCells] = None
         self._cells_ok = False                 # the index mirrors h / voronoi
         self._cells_next_build = 0
@@ -257,6 +260,7 @@ class ShardEngine:
         self.native.reset_ctl(self.state, int(n_sel), self._stream())
         self.n_host = int(n_sel)
         self._cells_ok = False
+        self._cells_scan_until = 0
 
     def _before_publish(self) -> None:
         # peer exchange: sequence s+1 may only be published once every peer's s has been seen
@@ -403,7 +407,8 @@ class ShardEngine:
             self._pick_body(rules, how)
 
     def _uses_cells(self, rules: int) -> bool:
-        return self.cells_enabled and self.n_host is not None and rules == RULE_NONE
+        return (self.cells_enabled and not self.cells_hold and self.n_host is not None
+                and (rules == RULE_NONE or self.cells_any_rules))
 
     def run_picks(self, n: int, rules: int = RULE_NONE) -> None:
         """Enqueue ``n`` farthest-point picks, replayed from CUDA graphs of 32, 16, ... 1 picks
@@ -517,6 +522,12 @@ class ShardEngine:
     def run_lane_picks(engines, n: int, rules: int) -> None:
         """``n`` lock-step picks on every engine of ``engines`` (graph-replayed on the GPU)."""
         e0 = engines[0]
+        if e0.mode == MODE_PRUNE and any(e._uses_cells(rules) for e in engines):
+            # prune mode steps the lanes one by one anyway (cs_fps_step_lanes); with a cell index each
+            # lane runs its own picks, through its own index
+            for e in engines:
+                e.run_picks(n, rules)
+            return
 
         def body():
             for e in engines:

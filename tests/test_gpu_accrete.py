@@ -86,3 +86,34 @@ def test_accrete_sharded_fused_lanes_match_reference(tmp_path):
     from tests.test_gpu_multi import _launch
     _launch(1, dict(mode="accrete", cases=[], out_dir=str(tmp_path)), timeout=1500,
             extra_env={"CORESETS_B200_MODE": "dense", "CORESETS_LANES_MIN_STEPS": "1"})
+
+
+SIM_CELLS = {"CORESETS_B200_CELLS_SIM_MIN_ROWS": "1", "CORESETS_B200_CELLS_SIM_MIN_STEPS": "1",
+             "CORESETS_B200_CELLS_MIN_ROWS": "1", "CORESETS_B200_CELLS_FIRST_BUILD": "3", "CORESETS_B200_CELLS_GROWTH": "1.4",
+             "CORESETS_B200_EARLY_DENSE_PICKS": "2", "CORESETS_B200_CELLS_GIVE_UP_SHARE": "2.0",
+             "CORESETS_B200_CELLS_PROBE_PICKS": "5", "CORESETS_B200_CELLS_LIVE_GATE": "2.0"}
+
+
+@pytest.mark.parametrize("name", ["acc_8192x32_k2048", "acc_mix_20000x64_k512_fps"])
+def test_accrete_probes_through_the_cell_index(name, tmp_path, monkeypatch):
+    """Single-GPU accretion with every bisect probe forced through the cell index (built per probe
+    from the reconstructed state, tiny and rebuilt often): lists and traces must stay the reference's."""
+    for k, v in SIM_CELLS.items():
+        monkeypatch.setenv(k, v)
+    test_accrete_matches_reference(name, tmp_path)
+
+
+def test_accrete_sharded_probes_through_the_cell_index(tmp_path):
+    """The sharded driver (default knobs and seeded walk with lanes) with probes on the cell index."""
+    from tests.test_gpu_multi import _launch
+    _launch(1, dict(mode="accrete", cases=[], out_dir=str(tmp_path)), timeout=1500,
+            extra_env=dict(SIM_CELLS, CORESETS_LANES_MIN_STEPS="1"))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_accrete_sharded_probes_through_the_cell_index_multi(tmp_path, world):
+    from tests.test_gpu_multi import _launch
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _launch(world, dict(mode="accrete", cases=[], out_dir=str(tmp_path)), timeout=1500,
+            extra_env=dict(SIM_CELLS, CORESETS_LANES_MIN_STEPS="1"))
