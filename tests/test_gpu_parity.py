@@ -338,7 +338,7 @@ def test_large_shard_properties():
 from pathlib import Path  # noqa: E402
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
-GOLDEN_CASES = sorted(p.stem for p in GOLDEN.glob("*.npz") if p.stem != "cpu_fps_c1" and not p.stem.startswith(("acc", "fullsize")))
+GOLDEN_CASES = sorted(p.stem for p in GOLDEN.glob("*.npz") if p.stem != "cpu_fps_c1" and not p.stem.startswith(("acc", "fullsize", "torch_")))
 
 
 @pytest.mark.parametrize("name", GOLDEN_CASES)

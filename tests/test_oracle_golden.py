@@ -17,7 +17,7 @@ from tests import data as tdata
 from tests.data import gaussian_mixture
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
-GPU_CASES = sorted(p.stem for p in GOLDEN.glob("*.npz") if p.stem != "cpu_fps_c1" and not p.stem.startswith(("acc", "fullsize")))
+GPU_CASES = sorted(p.stem for p in GOLDEN.glob("*.npz") if p.stem != "cpu_fps_c1" and not p.stem.startswith(("acc", "fullsize", "torch_")))
 
 
 def load_case(name):
