@@ -322,7 +322,7 @@ def roofline_of(kern_region, kern_all, rows_per_launch: int, dim: int, device, d
     peak, peak_kind = peaks()
     # DRAM traffic per row from the ncu captures under profiles/ (dram__bytes_read + write of one launch
     # divided by its rows; traffic grows in proportion to the rows of a launch)
-    per_row = {("tma", 128): 526.8, ("ldg", 128): 525.3, ("tma", 256): 1037.9, ("tma", 1024): 4118.0}.get((dense_kernel, dim))
+    per_row = {("tma", 128): 526.8, ("ldg", 128): 525.3, ("tma", 256): 1038.0, ("tma", 1024): 4117.7}.get((dense_kernel, dim))
     return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "peak_kind": peak_kind, "traffic": rows_per_launch * per_row if per_row else None,
             "traffic_source": (f"ncu dram__bytes_read+write of one launch on a 4-8 GB case at D = {dim} ({per_row} B/row, "
