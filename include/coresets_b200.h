@@ -267,7 +267,8 @@ CS_API int cs_pool_argmax(const float* h, const int64_t* pool, int64_t n_pool, i
  * block.  Each lane's arithmetic is that of cs_fps_step.  CS_MODE_DENSE and
  * CS_MODE_PRUNE_INLINE serve every lane from ONE pass over X; CS_MODE_PRUNE runs one
  * deferred-row step per lane, which is faster when few rows pass the triangle test.
- * Replaces voronoi_update_lanes_kernel (kernels/multi.cu:569-708).
+ * Replaces voronoi_update_lanes_kernel (kernels/multi.cu:569-708).  The control block's
+ * live_rows statistic is maintained by the per-lane steps only; the fused pass leaves it at 0.
  */
 CS_API int cs_fps_step_lanes(const cs_state* lanes, int32_t n_lanes, uint32_t mode, cs_stream stream);
 
