@@ -445,7 +445,7 @@ class ShardEngine:
                     self._replay(m, rules, "cells")
                     self._cells_probe_left -= m
                     if self._cells_probe_left == 0:
-                        self._judge_cells()
+                        self._assess_cells()
                 else:
                     self._replay(m, rules, "cells")
             n -= m
@@ -495,7 +495,7 @@ class ShardEngine:
         ctypes.memmove(ctypes.addressof(view), self._cells_meta_host.data_ptr(), _native.CELLS_META_BYTES)
         return view
 
-    def _judge_cells(self) -> None:
+    def _assess_cells(self) -> None:
         """After the first picks on a fresh index: if they visited most of it, the data does not
         separate into cells (or not yet) and the scan kernels take the rest of this epoch."""
         mv = self.read_cells_meta()
