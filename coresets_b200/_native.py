@@ -13,7 +13,7 @@ from typing import Optional
 
 from . import build as _build
 
-CS_ABI_VERSION = 7
+CS_ABI_VERSION = 8
 SELECT_SCRATCH_BYTES = 8192
 F_ELEMENT_ORDER = 1
 F_PDL = 2
@@ -29,6 +29,7 @@ MODE_PRUNE_INLINE = 2
 RULE_NONE = 0
 RULE_SIM_SINGLE = 1
 RULE_SIM_SHARDED = 2
+RULE_STOP_NONPOS = 3
 XCHG_GATHER = 0
 XCHG_PEER = 1
 MAX_PEERS = 8
@@ -37,7 +38,7 @@ EXPORTS = (
     "cs_version", "cs_error_string", "cs_last_cuda_error", "cs_device_check", "cs_init_state",
     "cs_reset_ctl", "cs_force_pick", "cs_commit_bound", "cs_fps_step", "cs_sim_begin",
     "cs_sim_final_check", "cs_xchg_window_words", "cs_xchg_wait", "cs_scan_argmax", "cs_fps_step_lanes", "cs_fps_step_noalloc",
-    "cs_select_kth_largest", "cs_pool_argmax", "cs_cells_build", "cs_cells_select", "cs_fps_step_cells", "cs_force_pick_list",
+    "cs_select_kth_largest", "cs_pool_argmax", "cs_cells_build", "cs_cells_select", "cs_fps_step_cells", "cs_force_pick_list", "cs_pool_pick",
 )
 
 
@@ -140,7 +141,8 @@ class CtlView(ctypes.Structure):
         ("last_val", ctypes.c_float),
         ("last_idx", ctypes.c_int32),
         ("xseq", ctypes.c_uint32),
-        ("reserved", ctypes.c_uint8 * (CS_CTL_BYTES - 60)),
+        ("halt", ctypes.c_int32),
+        ("reserved", ctypes.c_uint8 * (CS_CTL_BYTES - 64)),
     ]
 
 
@@ -179,6 +181,7 @@ class Native:
             ("cs_reset_ctl", [sp, ctypes.c_int32, vp]),
             ("cs_force_pick", [sp, ctypes.c_int64, ctypes.c_float, vp]),
             ("cs_force_pick_list", [sp, vp, vp, ctypes.c_float, vp]),
+            ("cs_pool_pick", [sp, vp, vp, vp]),
             ("cs_commit_bound", [sp, ctypes.c_uint32, vp]),
             ("cs_fps_step", [sp, ctypes.c_uint32, vp]),
             ("cs_sim_begin", [sp, ctypes.c_float, vp]),
@@ -227,6 +230,9 @@ class Native:
 
     def force_pick_list(self, s: CsState, list_ptr: int, vals_ptr, val: float, stream: int) -> None:
         self._check(self.lib.cs_force_pick_list(ctypes.byref(s), list_ptr, vals_ptr, val, stream), "cs_force_pick_list")
+
+    def pool_pick(self, s: CsState, pool_ptr: int, n_pool_ptr: int, stream: int) -> None:
+        self._check(self.lib.cs_pool_pick(ctypes.byref(s), pool_ptr, n_pool_ptr, stream), "cs_pool_pick")
 
     def commit_bound(self, s: CsState, rules: int, stream: int) -> None:
         self._check(self.lib.cs_commit_bound(ctypes.byref(s), rules, stream), "cs_commit_bound")

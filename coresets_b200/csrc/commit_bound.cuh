@@ -11,6 +11,7 @@ __global__ void __launch_bounds__(kThreads) commit_bound_kernel(const cs_state s
     extern __shared__ __align__(16) float s_cen[];
     Ctl* ctl = reinterpret_cast<Ctl*>(s.ctl);
     const int i = ctl->n_sel;
+    if (ctl->halt) return;                                 // a restricted run that ran dry
     if (i >= s.cap) {
         if (blockIdx.x == 0 && threadIdx.x == 0) ctl->status = ST_CAPACITY;
         return;
@@ -20,6 +21,11 @@ __global__ void __launch_bounds__(kThreads) commit_bound_kernel(const cs_state s
     const float val = key_val(w.key);
     const int64_t gidx = key_idx(w.key);
     const int D = s.D;
+    if (rules == CS_RULE_STOP_NONPOS && (gidx < 0 || val <= 0.0f)) {
+        // every block reaches the same verdict from the same candidates; nothing is committed
+        if (blockIdx.x == 0 && threadIdx.x == 0) ctl->halt = 1;
+        return;
+    }
 
     if (blockIdx.x == 0) {
         if (threadIdx.x == 0) {

@@ -21,6 +21,7 @@ struct Ctl {
     float last_val;
     int last_idx;
     unsigned xseq;      // peer exchange: sequence number of this rank's last published candidate
+    int halt;           // a restricted run found nothing positive to pick: later launches of the run do nothing
 };
 static_assert(sizeof(Ctl) <= CS_CTL_BYTES, "control block too large");
 static_assert(sizeof(cs_ctl_view) == CS_CTL_BYTES, "cs_ctl_view must span the control block");

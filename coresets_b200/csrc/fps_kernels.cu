@@ -301,6 +301,14 @@ int cs_force_pick(const cs_state* s, int64_t global_idx, float val, cs_stream st
     return check_launch();
 }
 
+int cs_pool_pick(const cs_state* s, const int64_t* pool, const int64_t* n_pool, cs_stream stream) {
+    int rc = validate(s);
+    if (rc) return rc;
+    if (!pool || !n_pool) return CS_E_ARG;
+    pool_pick_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(*s, pool, n_pool);
+    return check_launch();
+}
+
 int cs_force_pick_list(const cs_state* s, const int64_t* list, const float* vals, float val, cs_stream stream) {
     int rc = validate(s);
     if (rc) return rc;
@@ -312,7 +320,7 @@ int cs_force_pick_list(const cs_state* s, const int64_t* list, const float* vals
 int cs_commit_bound(const cs_state* s, uint32_t rules, cs_stream stream) {
     int rc = validate(s);
     if (rc) return rc;
-    if (rules > CS_RULE_SIM_SHARDED) return CS_E_ARG;
+    if (rules > CS_RULE_STOP_NONPOS) return CS_E_ARG;
     DevInfo d = device_info();
     if (!d.ok) return CS_E_DEVICE;
     const size_t smem = (size_t)s->D * sizeof(float);

@@ -49,6 +49,39 @@ __global__ void force_pick_list_kernel(const cs_state s, const int64_t* __restri
     force_pick_body(s, list[i], vals ? vals[i] : val);
 }
 
+// Restricted arg-max as the next pick's candidate: largest key over the rows of `pool` this shard
+// owns (one block; pools are at most a few thousand rows).
+__global__ void __launch_bounds__(1024) pool_pick_kernel(const cs_state s, const int64_t* __restrict__ pool,
+                                                        const int64_t* __restrict__ n_pool) {
+    __shared__ u64 s_best[32];
+    __shared__ u64 s_key;
+    Ctl* ctl = reinterpret_cast<Ctl*>(s.ctl);
+    const int i = ctl->n_sel;
+    if (ctl->halt || i >= s.cap) return;
+    const int64_t n = *n_pool;
+    u64 best = 0;
+    for (int64_t p = threadIdx.x; p < n; p += blockDim.x) {
+        const int64_t g = pool[p];
+        const int64_t l = g - s.shard_offset;
+        if (l >= 0 && l < s.N_local) {
+            const u64 k = make_key(s.h[l], g);
+            best = k > best ? k : best;
+        }
+    }
+    best = warp_max_key(best);
+    if ((threadIdx.x & 31) == 0) s_best[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        u64 bk = 0;
+        for (int q = 0; q < (int)(blockDim.x >> 5); ++q) bk = s_best[q] > bk ? s_best[q] : bk;
+        ctl->key[i & 1] = bk;
+        s_key = bk;
+    }
+    __syncthreads();
+    const u64 k = s_key;
+    if (s.world_size > 1) publish_candidate(s, ctl, k, key_idx(k) - s.shard_offset);
+}
+
 __global__ void sim_begin_kernel(Ctl* ctl, float sep) {
     ctl->viable = 0;
     ctl->steps = 0;

@@ -43,6 +43,7 @@ __global__ void __launch_bounds__(kThreads, CPL == 0 ? 2 : CS_MIN_BLOCKS) fps_st
 
     Ctl* ctl = reinterpret_cast<Ctl*>(s.ctl);
     const int i = ctl->n_sel;
+    if (ctl->halt) return;                                       // a restricted run that ran dry
     if (i >= s.cap) {
         if (blockIdx.x == 0 && threadIdx.x == 0) ctl->status = ST_CAPACITY;
         return;

@@ -381,8 +381,26 @@ class AccreteDriver:
         max_add = min(budget, len(desired))
         state = {"pool": torch.tensor(desired, dtype=torch.long, device=self.device), "dry": False}
 
+        device_walk = self.E.on_cuda and self.E.n_host is not None and _env_int("CORESETS_B200_DEVICE_FORWARD", 1) == 1
+
         def forward_to(n_picks: int) -> int:
             with self.timer("select_block_s"):
+                want = min(n_picks, max_add) - len(added)
+                if device_walk and want > 0 and not state["dry"]:
+                    # the whole walk on the device (the pool keeps its selected rows: they carry h = -1 and
+                    # can only win when nothing positive is left, which ends the walk)
+                    n0 = len(self.selected)
+                    made, dry = self.E.run_restricted(state["pool"], want)
+                    idxs = self.E.selected[n0 : n0 + made].tolist()
+                    vals = self.E.eps[n0 : n0 + made].tolist()
+                    for idx, val in zip(idxs, vals):
+                        self.sep = min(self.sep, val)
+                        step_seps.append(self.sep)
+                        added.append(int(idx))
+                        self.trace("forward", self._record(int(idx)), int(idx), val, self.sep)
+                    state["dry"] = dry or made < want
+                    self._key_valid = made > 0 and not dry
+                    return len(added)
                 while len(added) < min(n_picks, max_add) and not state["dry"]:
                     val, idx = self._restricted_argmax(state["pool"])
                     if val <= 0.0 or idx < 0:        # every remaining pool row is already selected

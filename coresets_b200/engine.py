@@ -17,7 +17,8 @@ import torch
 import torch.distributed as dist
 
 from . import _native
-from ._native import CsCells, CsState, CtlView, MODE_DENSE, MODE_PRUNE, RULE_NONE, XCHG_GATHER, XCHG_PEER
+from ._native import (CsCells, CsState, CtlView, MODE_DENSE, MODE_PRUNE, RULE_NONE, RULE_STOP_NONPOS, XCHG_GATHER,
+                      XCHG_PEER)
 
 _NORM_CHUNK_ELEMS = 1 << 28  # elements of the X*X temporary per chunk (1 GiB of fp32)
 
@@ -309,6 +310,11 @@ class ShardEngine:
             self.native.force_pick_list(self.state, self._forced_list.data_ptr(), self._forced_vals.data_ptr(),
                                         float("inf"), self._stream())
             how = None
+        elif how == "pool":
+            if self.world_size > 1 and self.xchg == XCHG_PEER:
+                self.native.xchg_wait(self.state, self._stream())     # see _before_publish
+            self.native.pool_pick(self.state, self._pool_buf.data_ptr(), self._pool_n.data_ptr(), self._stream())
+            how = None
         self.exchange()
         self.commit(rules)
         if how == "cells":
@@ -348,6 +354,39 @@ class ShardEngine:
         self._forced_list[lo:hi] = torch.tensor(idx, dtype=torch.int64).to(self.device)
         self._forced_vals[lo:hi] = torch.tensor(vals, dtype=torch.float32).to(self.device)
         self._replay(len(idx), rules, "forced")
+
+    def run_restricted(self, pool: torch.Tensor, n: int):
+        """Up to ``n`` greedy picks restricted to the global rows in ``pool`` (int64, on the device):
+        each takes the largest ``h`` among the pool's rows (ties to the smaller index), commits it
+        and runs its update -- the forward walk of accretion (block_forward.py:38-53,
+        sharded.py:174-215) without a host round trip per pick.  The run stops by itself when the
+        best value is not positive.  Returns ``(picks made, ran dry)``; one read-back."""
+        if not (self.on_cuda and self.n_host is not None):
+            raise RuntimeError("run_restricted needs a CUDA engine whose pick count the host knows")
+        n = int(n)
+        if n <= 0:
+            return 0, False
+        if not hasattr(self, "_pool_buf"):
+            self._pool_buf = torch.zeros(max(self.cap, 1), dtype=torch.int64, device=self.device)
+            self._pool_n = torch.zeros(1, dtype=torch.int64, device=self.device)
+        if pool.numel() > self._pool_buf.numel():
+            self._pool_buf = torch.zeros(int(pool.numel()), dtype=torch.int64, device=self.device)
+            self._graphs = {k: g for k, g in self._graphs.items() if k[2] != "pool"}
+        self._pool_buf[: pool.numel()].copy_(pool)
+        self._pool_n.fill_(int(pool.numel()))
+        before = self.n_host
+        n = min(n, self.cap - before)
+        self._replay(n, RULE_STOP_NONPOS, "pool")
+        ctl = self.read_ctl()
+        made = int(ctl.n_sel) - before
+        self.n_host = int(ctl.n_sel)
+        dry = bool(ctl.halt)
+        if dry:
+            # the halt word silences every later launch: clear it (and with it the key slots, so the
+            # caller recomputes the key before the next free pick)
+            self.reset_ctl(self.n_host)
+            self._unconsumed = False
+        return made, dry
 
     def _graph(self, n: int, rules: int, how=None):
         key = (n, rules, self.mode if how is None else how)

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define CS_ABI_VERSION 7
+#define CS_ABI_VERSION 8
 
 #if defined(__GNUC__)
 #define CS_API __attribute__((visibility("default")))
@@ -71,6 +71,9 @@ extern "C" {
 #define CS_RULE_NONE 0u    /* plain FPS: no separation bookkeeping */
 #define CS_RULE_SIM_SINGLE 1u   /* commit_center_with_sep_kernel rules (commit.cu:41-51) */
 #define CS_RULE_SIM_SHARDED 2u  /* reduce_and_commit_multi_sharded_kernel rules (multi.cu:331-340) */
+#define CS_RULE_STOP_NONPOS 3u  /* restricted forward walk of accretion: a winner whose value is not
+                                   positive (or no winner) is NOT committed; the control block's halt
+                                   word is set instead (block_forward.py:45-47, _base.py:419-421) */
 
 /* how the per-pick candidates travel between ranks (cs_state.xchg) */
 #define CS_XCHG_GATHER 0   /* cs_fps_step writes pack_local; the caller all-gathers into pack_all */
@@ -96,7 +99,9 @@ typedef struct cs_ctl_view {
     float last_val;      /* value (max h) of the last committed pick                          */
     int32_t last_idx;    /* global index of the last committed pick (-1: nothing left)       */
     uint32_t xseq;       /* peer exchange: sequence number of the last published candidate   */
-    uint8_t reserved[CS_CTL_BYTES - 60];
+    int32_t halt;        /* 1 once a CS_RULE_STOP_NONPOS commit met a best value <= 0: commits and
+                            steps launched after it do nothing until cs_reset_ctl                  */
+    uint8_t reserved[CS_CTL_BYTES - 64];
 } cs_ctl_view;
 
 /*
@@ -165,6 +170,18 @@ CS_API int cs_reset_ctl(const cs_state* s, int32_t n_sel, cs_stream stream);
  * cs_commit_bound and cs_fps_step exactly like a normal pick.
  */
 CS_API int cs_force_pick(const cs_state* s, int64_t global_idx, float val, cs_stream stream);
+
+/*
+ * Make the next pick the arg-max of h over a list of global rows (value first, then the smaller
+ * index): pool[0 .. *n_pool) are global row indices, both in device memory; rows of other shards are
+ * ignored, the owner ranks publish their best, the others "nothing".  Follow with the all-gather
+ * (world_size > 1), cs_commit_bound(CS_RULE_STOP_NONPOS) and cs_fps_step like a normal pick; nothing
+ * goes through the host, so a run of restricted picks replays from a CUDA graph and stops by itself
+ * (halt) when the pool has nothing positive left.  Replaces the per-pick mask / gather / max /
+ * all-gather / .item() sequence of the accretion forward loop (cuda/_internal/block_forward.py:38-53,
+ * cuda/multi/sharded.py:174-215).
+ */
+CS_API int cs_pool_pick(const cs_state* s, const int64_t* pool, const int64_t* n_pool, cs_stream stream);
 
 /*
  * cs_force_pick with the row read on the device: the next pick becomes list[n_sel] (a device array

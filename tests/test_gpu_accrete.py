@@ -117,3 +117,45 @@ def test_accrete_sharded_probes_through_the_cell_index_multi(tmp_path, world):
         pytest.skip(f"needs {world} GPUs")
     _launch(world, dict(mode="accrete", cases=[], out_dir=str(tmp_path)), timeout=1500,
             extra_env=dict(SIM_CELLS, CORESETS_LANES_MIN_STEPS="1"))
+
+
+@pytest.mark.parametrize("name", ["acc_8192x32_k2048", "acc_mix_20000x64_k512_fps"])
+def test_accrete_with_the_forward_walk_on_the_host(name, tmp_path, monkeypatch):
+    """The forward walk runs on the device by default (cs_pool_pick + CS_RULE_STOP_NONPOS, replayed
+    from graphs); the per-pick host loop it replaces must give the same lists and traces."""
+    monkeypatch.setenv("CORESETS_B200_DEVICE_FORWARD", "0")
+    test_accrete_matches_reference(name, tmp_path)
+
+
+def test_restricted_run_stops_when_the_pool_runs_dry():
+    """run_restricted on a pool smaller than the request: it commits the pool's rows in greedy
+    order, stops by itself, reports `dry`, and leaves the engine usable for free picks."""
+    from coresets_b200 import engine
+    from tests.data import gaussian_mixture
+    X = torch.from_numpy(gaussian_mixture(3000, 32, 6, seed=1)).cuda()
+    norms = engine.row_norms(X)
+    eng = engine.ShardEngine(X, norms, 64)
+    eng.init_state()
+    eng.pick_forced(5)
+    pool = torch.tensor([10, 11, 12, 5, 2000, 2500], dtype=torch.long, device="cuda")
+    made, dry = eng.run_restricted(pool, 4)
+    assert (made, dry) == (4, False)
+    made2, dry2 = eng.run_restricted(pool, 10)
+    assert dry2 and made2 == 1                      # one unselected row was left; row 5 was the seed
+    picked = eng.selected[:6].tolist()
+    assert picked[0] == 5 and sorted(picked[1:]) == [10, 11, 12, 2000, 2500]
+    # greedy order: every pick had the largest h of the rows still unselected in the pool
+    ref = engine.ShardEngine(X, norms, 64)
+    ref.init_state()
+    ref.pick_forced(5)
+    left = {10, 11, 12, 2000, 2500}
+    for want in picked[1:]:
+        h = ref.h.cpu()
+        best = max(left, key=lambda r: (float(h[r]), -r))
+        assert best == want
+        ref.pick_forced(best, float(h[best]))
+        left.remove(best)
+    assert torch.equal(ref.h.view(torch.int32), eng.h.view(torch.int32))
+    eng.scan()
+    eng.run_picks(3)
+    assert eng.check_status().n_sel == 9

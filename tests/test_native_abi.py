@@ -51,3 +51,12 @@ def test_decode_key_round_trip():
     # a key read back as a signed 64-bit integer decodes the same
     k = make_key(np.float32(5.0), 77)
     assert _native.decode_key(k - (1 << 64)) == (5.0, 77)
+
+
+def test_typed_wrapper_binds_every_entry_point():
+    """`_native.Native()` loads the library, checks the ABI version and sets the argument types of
+    every entry point it wraps (no GPU needed: nothing is called)."""
+    n = _native.Native()
+    assert n.lib.cs_version() == _native.CS_ABI_VERSION
+    for name in _native.EXPORTS:
+        assert hasattr(n.lib, name), name
