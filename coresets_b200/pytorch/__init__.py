@@ -2,6 +2,7 @@
 matrix-vector product per pick.  Not the accelerated path -- ``fps_cuda`` / ``fps_sharded`` never
 come through here -- but part of the package's public names (``coresets.fps``)."""
 from .accrete import accrete
+from .accrete_distributed import accrete as accrete_distributed
 from .fps import fps, fps_update, voronoi_fps
 
-__all__ = ["accrete", "fps", "fps_update", "voronoi_fps"]
+__all__ = ["accrete", "accrete_distributed", "fps", "fps_update", "voronoi_fps"]

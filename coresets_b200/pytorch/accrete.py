@@ -28,17 +28,20 @@ class _State:
     """``h`` (squared distance to the nearest pick, -1 on picks), the cell of every row and the table
     of picked rows, advanced one pick at a time."""
 
-    def __init__(self, X: Tensor, capacity: int):
+    def __init__(self, X: Tensor):
         n, dim = X.shape
-        opts = dict(dtype=X.dtype, device=X.device)
+        self.n_rows, self.dim, self.device = n, dim, X.device
+        self.opts = dict(dtype=X.dtype, device=X.device)
         self.X = X
         self.norms = (X * X).sum(dim=1)
-        self.h = torch.full((n,), float("inf"), **opts)
+        self.h = torch.full((n,), float("inf"), **self.opts)
         self.cell = torch.zeros(n, dtype=torch.long, device=X.device)
-        self.scratch = torch.empty(n, **opts)
-        self.centres = torch.empty((capacity, dim), **opts)
-        self.centre_norms = torch.empty(capacity, **opts)
+        self.scratch = torch.empty(n, **self.opts)
         self.dense_above = int(0.5 * n)
+
+    def reserve(self, capacity: int) -> None:
+        self.centres = torch.empty((capacity, self.dim), **self.opts)
+        self.centre_norms = torch.empty(capacity, **self.opts)
 
     def dense(self, h: Tensor, cell: Tensor, row: int, pos: int) -> None:
         """Dense update of (h, cell) for the pick ``row`` at position ``pos`` (fps.py:8-28)."""
@@ -106,8 +109,8 @@ class _State:
                               added: List[int], seps: List[float], budget: int) -> int:
         """Binary search over the walk's prefixes (phases.py:142-225); a prefix ``m`` is viable when a fill
         of ``budget - m`` unrestricted picks ends with separation above coverage."""
-        n = self.X.shape[0]
-        cell_unused = torch.zeros(n, dtype=torch.long, device=self.X.device)
+        n = self.n_rows
+        cell_unused = torch.zeros(n, dtype=torch.long, device=self.device)
         lo, hi, best = 0, len(added), 0
         while lo <= hi:
             m = (lo + hi) // 2
@@ -141,18 +144,13 @@ class _State:
         return best
 
 
-def accrete(X_anchor: Tensor, X_candidates: Tensor, anchor_order: Tensor, candidate_order: Tensor,
-            max_k: Optional[int] = None, verbose: bool = True) -> Tensor:
-    """int64 indices over ``cat(X_anchor, X_candidates)`` in selection order (indices below
-    ``len(X_anchor)`` are anchors).  ``candidate_order`` is unused, kept for the reference's signature."""
-    n_anchor = X_anchor.shape[0]
-    X = torch.cat([X_anchor, X_candidates], dim=0)
-    n = X.shape[0]
+def _run(st: "_State", order, n_anchor: int, max_k: Optional[int], talk: bool, label: str) -> Tensor:
+    """The accretion loop over a state (local or sharded); ``order`` lists the anchors' global rows."""
+    n = st.n_rows
     if max_k is None:
         max_k = int(math.log2(n))
-    order = anchor_order.tolist()
     blocks = [set(order[: min(2 ** i, n_anchor)]) for i in range(1, max_k + 1)]
-    st = _State(X, 2 ** max_k)
+    st.reserve(2 ** max_k)
     picked: List[int] = [order[0]]
     picked_set = {order[0]}
     sep = float("inf")
@@ -163,7 +161,7 @@ def accrete(X_anchor: Tensor, X_candidates: Tensor, anchor_order: Tensor, candid
         picked_set.add(row)
         st.commit(row, len(picked) - 1)
 
-    if verbose:
+    if talk:
         print(f"{'k':<4} | {'size':<6} | {'in_Bk':>6} | {'from_A':>7} | {'from_C':>7} | "
               f"{'sep':>9} | {'cov':>9} | {'rel_gap':>11}")
         print("-" * 79)
@@ -183,7 +181,7 @@ def accrete(X_anchor: Tensor, X_candidates: Tensor, anchor_order: Tensor, candid
             added: List[int] = []
             seps: List[float] = [sep_snap]
             for _ in range(min(budget, len(pool))):              # greedy walk restricted to the pool
-                at = int(torch.argmax(st.h[torch.tensor(pool, dtype=torch.long, device=X.device)]).item())
+                at = int(torch.argmax(st.h[torch.tensor(pool, dtype=torch.long, device=st.device)]).item())
                 row = pool[at]
                 val = float(st.h[row].item())
                 if val <= 0:
@@ -217,14 +215,22 @@ def accrete(X_anchor: Tensor, X_candidates: Tensor, anchor_order: Tensor, candid
         rel_gap = (sep / cov_sq - 1.0) if (cov_sq > 0 and math.isfinite(sep)) else float("inf")
         if math.isfinite(sep) and sep < cov_sq * (1.0 - 1e-3):
             raise RuntimeError(
-                f"accrete: sep > cov violated at k={k} (size={size}): "
+                f"{label}: sep > cov violated at k={k} (size={size}): "
                 f"sep={sep_val:.8e}, cov={cov_val:.8e}, rel_gap={rel_gap:.3e}. "
                 "Gross violation, not float noise."
             )
-        if verbose:
+        if talk:
             layer = set(picked[:size])
             from_a = sum(1 for s in layer if s < n_anchor)
             gap = f"{rel_gap:>11.3e}" if math.isfinite(rel_gap) else f"{'inf':>11}"
             print(f"{k:<4} | {size:<6} | {len(layer & blocks[k - 1]):>6} | {from_a:>7} | {size - from_a:>7} | "
                   f"{sep_val:>9.5f} | {cov_val:>9.5f} | {gap}")
-    return torch.tensor(picked, dtype=torch.long, device=X.device)
+    return torch.tensor(picked, dtype=torch.long, device=st.device)
+
+
+def accrete(X_anchor: Tensor, X_candidates: Tensor, anchor_order: Tensor, candidate_order: Tensor,
+            max_k: Optional[int] = None, verbose: bool = True) -> Tensor:
+    """int64 indices over ``cat(X_anchor, X_candidates)`` in selection order (indices below
+    ``len(X_anchor)`` are anchors).  ``candidate_order`` is unused, kept for the reference's signature."""
+    st = _State(torch.cat([X_anchor, X_candidates], dim=0))
+    return _run(st, anchor_order.tolist(), int(X_anchor.shape[0]), max_k, verbose, "accrete")
