@@ -13,10 +13,11 @@ from typing import Optional
 
 from . import build as _build
 
-CS_ABI_VERSION = 8
+CS_ABI_VERSION = 9
 SELECT_SCRATCH_BYTES = 8192
 F_ELEMENT_ORDER = 1
 F_PDL = 2
+F_X_HALF = 4
 F_TEST_STALL_PIPE = 0x100
 CS_CTL_BYTES = 256
 CELL_TILE = 256

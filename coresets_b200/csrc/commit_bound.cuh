@@ -57,13 +57,13 @@ __global__ void __launch_bounds__(kThreads) commit_bound_kernel(const cs_state s
         }
         if (gidx >= 0) {
             float* dst = s.X_sel + (int64_t)i * D;
-            for (int c = threadIdx.x; c < D; c += blockDim.x) dst[c] = w.row[c];
+            for (int c = threadIdx.x; c < D; c += blockDim.x) dst[c] = winner_elem(s, w, c);
         }
     }
     if (gidx < 0 || i == 0) return;
 
     // dSL_quarter[v] = |X_sel[v] - x_new|^2 / 4 for every old centre (commit.cu:69-102)
-    for (int c = threadIdx.x; c < D; c += blockDim.x) s_cen[c] = w.row[c];
+    for (int c = threadIdx.x; c < D; c += blockDim.x) s_cen[c] = winner_elem(s, w, c);
     __syncthreads();
     const int lane = threadIdx.x & 31;
     const int gw = blockIdx.x * kWarps + (threadIdx.x >> 5);

@@ -25,7 +25,10 @@ __device__ __forceinline__ unsigned long long global_ns() {
 // All threads of ONE block call this.  k == 0 publishes "nothing"; l is the local row of the key.
 __device__ void publish_candidate(const cs_state& s, Ctl* ctl, const u64 k, const int64_t l) {
     const int D = s.D;
-    const uint32_t* src = reinterpret_cast<const uint32_t*>(s.X + (k ? l : 0) * (int64_t)D);
+    // the candidate row travels as float32 bit patterns; half rows widen losslessly (multi.cu:245)
+    const bool half_rows = (s.flags & CS_F_X_HALF) != 0;
+    const int64_t lrow = k ? l : 0;
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(s.X + (half_rows ? 0 : lrow * (int64_t)D));
     const uint32_t norm_bits = k ? __float_as_uint(s.norms[l]) : 0u;
     if (s.xchg == CS_XCHG_GATHER) {
         uint32_t* p = s.pack_local;
@@ -35,7 +38,8 @@ __device__ void publish_candidate(const cs_state& s, Ctl* ctl, const u64 k, cons
             p[2] = norm_bits;
             p[3] = 0u;
         }
-        for (int c = threadIdx.x; c < D; c += blockDim.x) p[4 + c] = k ? src[c] : 0u;
+        for (int c = threadIdx.x; c < D; c += blockDim.x)
+            p[4 + c] = k ? (half_rows ? __float_as_uint(x_elem(s, lrow, c)) : src[c]) : 0u;
         return;
     }
     const unsigned seq = ctl->xseq + 1u;
@@ -49,7 +53,8 @@ __device__ void publish_candidate(const cs_state& s, Ctl* ctl, const u64 k, cons
             p[2] = norm_bits;
             p[3] = 0u;
         }
-        for (int c = threadIdx.x; c < D; c += blockDim.x) p[4 + c] = k ? src[c] : 0u;
+        for (int c = threadIdx.x; c < D; c += blockDim.x)
+            p[4 + c] = k ? (half_rows ? __float_as_uint(x_elem(s, lrow, c)) : src[c]) : 0u;
     }
     __threadfence_system();              // every writer orders its stores before the barrier
     __syncthreads();
@@ -98,18 +103,25 @@ __global__ void xchg_wait_kernel(const cs_state s) {
 // ---- winner resolution shared by commit_bound and sim_final_check -------------------------
 struct Winner {
     u64 key;
-    const float* row;   // D floats (in X or in the gathered packs)
+    const float* row;   // D floats (in X or in the gathered packs); null when the row is a half row of X
+    int64_t xrow;       // local row of X when the winner is this rank's own row (world_size 1)
     float norm;
 };
+// Element c of the winner's row.
+__device__ __forceinline__ float winner_elem(const cs_state& s, const Winner& w, const int c) {
+    return w.row ? w.row[c] : x_elem(s, w.xrow, c);
+}
 __device__ __forceinline__ Winner resolve_winner(const cs_state& s, const Ctl* ctl, int i, const uint32_t* packs) {
     Winner w;
     w.row = nullptr;
+    w.xrow = 0;
     w.norm = 0.0f;
     if (s.world_size <= 1) {
         w.key = ctl->key[i & 1];
         if (w.key) {
             int64_t l = key_idx(w.key) - s.shard_offset;
-            w.row = s.X + l * (int64_t)s.D;
+            w.row = (s.flags & CS_F_X_HALF) ? nullptr : s.X + l * (int64_t)s.D;
+            w.xrow = l;
             w.norm = s.norms[l];
         }
     } else {

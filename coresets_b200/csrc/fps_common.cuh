@@ -113,6 +113,19 @@ __device__ __forceinline__ void pdl_enter() {
 
 __device__ __forceinline__ float4 ld_stream4(const float4* p) { return __ldcs(p); }
 
+// Element c of local row `row` of X as a float: float32 rows, or half rows widened on the fly.
+__device__ __forceinline__ float x_elem(const cs_state& s, const int64_t row, const int c) {
+    if (s.flags & CS_F_X_HALF) return __half2float(__ldg(reinterpret_cast<const __half*>(s.X) + row * (int64_t)s.D + c));
+    return __ldg(s.X + row * (int64_t)s.D + c);
+}
+
+// Element-wise warp dot of a half row with the centre (one fma per element, _shared.cuh:52-58).
+__device__ __forceinline__ float warp_dot_half(const __half* __restrict__ row, const float* __restrict__ cen, int D, int lane) {
+    float acc = 0.0f;
+    for (int c = lane; c < D; c += 32) acc = __fmaf_rn(__half2float(__ldg(row + c)), cen[c], acc);
+    return warp_tree_sum(acc);
+}
+
 // Generic warp dot: row in global memory, centre anywhere (shared or global); any D.
 __device__ __forceinline__ float warp_dot_generic(const float* __restrict__ row,
                                                   const float* __restrict__ cen, int D, int lane,

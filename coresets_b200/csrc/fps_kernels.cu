@@ -23,6 +23,7 @@
 // builds with --use_fast_math (src/coresets/cuda/extension.py:63).
 #include "coresets_b200.h"
 
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -143,10 +144,11 @@ int validate(const cs_state* s) {
         for (int r = 0; r < s->world_size; ++r)
             if (!s->peer_win[r] || ((uintptr_t)s->peer_win[r] & 15u)) return CS_E_ARG;
     }
+    if ((s->flags & CS_F_X_HALF) && !(s->flags & CS_F_ELEMENT_ORDER)) return CS_E_ARG;
     if (s->shard_offset + s->N_local >= (int64_t)1 << 31) return CS_E_RANGE;
     if (s->cap >= (int64_t)1 << 31) return CS_E_RANGE;
     if ((s->D & 3) == 0) {
-        if (((uintptr_t)s->X | (uintptr_t)s->X_sel) & 15u) return CS_E_ALIGN;
+        if ((((s->flags & CS_F_X_HALF) ? 0 : (uintptr_t)s->X) | (uintptr_t)s->X_sel) & 15u) return CS_E_ALIGN;
         if (s->world_size > 1 && s->xchg == CS_XCHG_GATHER &&
             (((uintptr_t)s->pack_local | (uintptr_t)s->pack_all) & 15u)) return CS_E_ALIGN;
     }

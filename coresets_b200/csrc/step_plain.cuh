@@ -214,7 +214,10 @@ __global__ void __launch_bounds__(kThreads, CS_MIN_BLOCKS) fps_step_kernel(const
                 while (mm) {
                     const int r = __ffs(mm) - 1;
                     mm &= mm - 1;
-                    float p = warp_dot_generic(s.X + (base + j + (int64_t)r * kRowsPerLane) * (int64_t)D, s_cen, D, lane, element_order);
+                    const int64_t xr = base + j + (int64_t)r * kRowsPerLane;
+                    float p = (s.flags & CS_F_X_HALF)
+                                  ? warp_dot_half(reinterpret_cast<const __half*>(s.X) + xr * (int64_t)D, s_cen, D, lane)
+                                  : warp_dot_generic(s.X + xr * (int64_t)D, s_cen, D, lane, element_order);
                     if (lane == r) dj = p;
                 }
             }

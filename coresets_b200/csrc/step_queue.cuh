@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(kThreads, CPL == 0 ? 2 : CS_MIN_BLOCKS) fps_st
     }
     // chunked order needs whole 16-byte chunks and is what float32 inputs get (_shared.cuh:41-50)
     const bool chunked = (D & 3) == 0 && !(s.flags & CS_F_ELEMENT_ORDER);
+    const bool half_rows = (s.flags & CS_F_X_HALF) != 0;
     const int nb = i < n_bound_smem ? i : n_bound_smem;
     // voronoi <= i (the row committed for this pick carries i itself), so with i inside the staged
     // table every look-up stays within the block's shared memory
@@ -116,7 +117,9 @@ __global__ void __launch_bounds__(kThreads, CPL == 0 ? 2 : CS_MIN_BLOCKS) fps_st
                 for (int c = lane; c < D; c += 32) {                 // _shared.cuh:52-58: one fma per element
                     float a[4];
 #pragma unroll
-                    for (int b = 0; b < 4; ++b) a[b] = __ldcs(s.X + (int64_t)rows[b] * D + c);
+                    for (int b = 0; b < 4; ++b)
+                        a[b] = half_rows ? __half2float(__ldcs(reinterpret_cast<const __half*>(s.X) + (int64_t)rows[b] * D + c))
+                                         : __ldcs(s.X + (int64_t)rows[b] * D + c);
                     const float cc = s_cen[c];
 #pragma unroll
                     for (int b = 0; b < 4; ++b) acc[b] = __fmaf_rn(a[b], cc, acc[b]);

@@ -213,8 +213,9 @@ class AccreteDriver:
                 else:
                     X_added = self.E.X_sel[n_snap : n_snap + m]
                     n_added = self.E.norms_sel[n_snap : n_snap + m]
-                    X_aff = self.E.X[affected]
-                    if self.X_src is not None:
+                    if self.X_src is None:
+                        X_aff = self.E.X[affected]
+                    else:
                         # float16 / float64 input: the product runs in the caller's dtype.  The
                         # single-GPU reference gathers the added rows from X (reconstruct.py:102),
                         # the sharded one keeps them in an X_sel of X's dtype that was filled from

@@ -48,16 +48,20 @@ _CONVERT_CHUNK_ELEMS = 1 << 28
 
 
 def engine_matrix(X: torch.Tensor):
-    """Return ``(X32, element_order)``: the float32 row-major matrix the kernels read and whether
+    """Return ``(X_kernels, element_order)``: the row-major matrix the kernels read and whether
     its dots must be summed element-wise.
 
     The reference dispatches float32, float64 and float16 (``AT_DISPATCH_FLOATING_TYPES_AND_HALF``,
     src/coresets/cuda/kernels/warp.cu:167) and for the last two converts every element to float
     before an element-wise fma chain (``_shared.cuh:55-58``).  Converting the matrix once gives
     the same float values (float16 -> float32 is exact, float64 -> float32 rounds to nearest as
-    the kernel's cast does), so those inputs run the float32 kernels with the element-wise order."""
+    the kernel's cast does), so those inputs run the float32 kernels with the element-wise order.
+    float16 rows on the device are read where they lie (``CS_F_X_HALF``: every element widened at the
+    load, 2 bytes of HBM per element and no float32 copy); ``CORESETS_B200_NATIVE_HALF=0`` converts."""
     if X.dtype == torch.float32:
         return X.contiguous(), False
+    if X.dtype == torch.float16 and X.is_cuda and _knob("NATIVE_HALF", 1):
+        return X.contiguous(), True
     if X.dtype not in (torch.float16, torch.float64):
         raise ValueError(f"X must be float32, float64 or float16 (the reference's dispatch), got {X.dtype}")
     N, D = X.shape
@@ -127,8 +131,10 @@ class ShardEngine:
                  cells_any_rules: bool = False):
         if X_local.dim() != 2:
             raise ValueError(f"X_local must be 2-D, got shape {tuple(X_local.shape)}")
-        if X_local.dtype != torch.float32:
-            raise ValueError(f"the engine reads float32 rows (see engine_matrix), got {X_local.dtype}")
+        self.half_rows = X_local.dtype == torch.float16
+        if X_local.dtype != torch.float32 and not (self.half_rows and element_order and X_local.is_cuda):
+            raise ValueError("the engine reads float32 rows, or float16 rows on the device with the element-wise "
+                             f"order (see engine_matrix), got {X_local.dtype}")
         if not X_local.is_contiguous():
             raise ValueError("X_local must be contiguous (row-major)")
         self.native = _native.get_native()
@@ -234,6 +240,7 @@ class ShardEngine:
             s.peer_win[r] = ptr
         s.xchg_timeout_ms = int(os.environ.get("CORESETS_B200_XCHG_TIMEOUT_MS", "10000"))
         s.flags = ((_native.F_ELEMENT_ORDER if self.element_order else 0) | self._extra_flags
+                   | (_native.F_X_HALF if self.half_rows else 0)
                    | (_native.F_PDL if self.on_cuda and _knob("PDL", 1) else 0))
         return s
 

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define CS_ABI_VERSION 8
+#define CS_ABI_VERSION 9
 
 #if defined(__GNUC__)
 #define CS_API __attribute__((visibility("default")))
@@ -61,6 +61,10 @@ extern "C" {
                               ... with one fma each) even when D % 4 == 0: the order the reference uses
                               for float16 / float64 inputs (_shared.cuh:55-58), whose rows the caller
                               passes converted to float32 */
+#define CS_F_X_HALF 4u       /* X holds IEEE half rows (2 bytes per element, row-major, no alignment rule);
+                              every element is widened to float where it is read, which is what the
+                              reference's half instantiation does (_shared.cuh:55-58).  Requires
+                              CS_F_ELEMENT_ORDER.  X_sel, the packs and every other array stay float32 */
 #define CS_F_PDL 2u          /* launch the kernels of a pick (commit, cell selection, scan, evaluation, the
                               prune-mode step) as programmatic dependents of the kernel before them on the
                               stream: their start overlaps the predecessor's tail, they read nothing
@@ -109,7 +113,7 @@ typedef struct cs_ctl_view {
  * A candidate pack is (4 + D) 32-bit words: key low, key high, norm bits, 0, row bits[D].
  */
 typedef struct cs_state {
-    const float* X;        /* [N_local, D] row-major fp32                                     */
+    const float* X;        /* [N_local, D] row-major fp32 (IEEE half with CS_F_X_HALF)            */
     const float* norms;    /* [N_local] squared row norms                                     */
     float* h;              /* [N_local] squared distance to nearest centre; -1 = selected     */
     int32_t* voronoi;      /* [N_local] slot of the nearest centre (reference: int64)         */

@@ -120,6 +120,43 @@ def test_float16_and_float64_inputs(dtype, N, D, k, mode):
     assert_matches_oracle(eng, X, norms, k)
 
 
+@pytest.mark.parametrize("N,D,k", [(3000, 128, 200), (1501, 50, 64), (2000, 7, 100), (600, 1028, 40), (777, 1, 30)])
+@pytest.mark.parametrize("mode", [MODE_PRUNE, MODE_DENSE])
+def test_half_rows_read_in_place_equal_the_converted_matrix(N, D, k, mode, monkeypatch):
+    """float16 rows on the device are read where they lie (CS_F_X_HALF), odd row widths and
+    therefore 2-byte aligned rows included; same bits as the run over a float32 copy."""
+    from tests.data import as_dtype
+    X = as_dtype(gaussian_mixture(N, D, 8, seed=N + D), "float16")
+    a, norms = run_engine(X, k, mode=mode)
+    assert a.X.dtype == torch.float16 and a.half_rows
+    monkeypatch.setenv("CORESETS_B200_NATIVE_HALF", "0")
+    b, _ = run_engine(X, k, mode=mode)
+    assert b.X.dtype == torch.float32 and not b.half_rows
+    assert torch.equal(a.selected, b.selected) and torch.equal(a.eps.view(torch.int32), b.eps.view(torch.int32))
+    assert torch.equal(a.h.view(torch.int32), b.h.view(torch.int32)) and torch.equal(a.voronoi, b.voronoi)
+    assert torch.equal(a.X_sel.view(torch.int32), b.X_sel.view(torch.int32))
+    assert_matches_oracle(a, X, norms, k)
+
+
+@pytest.mark.parametrize("sizes,D", [([1000, 1003], 64), ([0, 700, 0, 650], 50), ([301, 299, 2, 300], 129)])
+def test_half_rows_multi_rank_kernels_on_one_device(sizes, D):
+    """Half rows with world_size > 1: the candidate row travels widened to float32 (multi.cu:245)."""
+    from tests.data import as_dtype
+    N, k = sum(sizes), 100
+    X = as_dtype(with_duplicates(gaussian_mixture(N, D, 8, seed=N + D), 20, seed=2), "float16")
+    engs, norms, offs = _emulate_ranks(X, sizes, k, first=3)
+    assert all(e.half_rows for e in engs)
+    with oracle.element_order():
+        o_sel, o_eps, o_h, o_v = oracle.fps_sharded(X.astype(np.float32), norms, k, sizes, first=3)
+    for r, e in enumerate(engs):
+        assert e.check_status().n_sel == k
+        np.testing.assert_array_equal(e.selected.cpu().numpy(), o_sel)
+        np.testing.assert_array_equal(bits(e.eps.cpu().numpy()), bits(o_eps))
+        n = sizes[r]
+        np.testing.assert_array_equal(bits(e.h[:n].cpu().numpy()), bits(o_h[offs[r] : offs[r] + n]))
+        np.testing.assert_array_equal(e.voronoi[:n].cpu().numpy().astype(np.int64), o_v[offs[r] : offs[r] + n])
+
+
 def test_fps_cuda_accepts_float16_and_float64():
     from tests.data import as_dtype
     import coresets_b200
@@ -231,11 +268,12 @@ def _emulate_ranks(X_np, sizes, k, first=0, mode=MODE_PRUNE):
     offs = np.concatenate([[0], np.cumsum(sizes)[:-1]]).tolist()
     X = torch.from_numpy(X_np).to(dev)
     norms = engine.row_norms(X)
+    X, element_order = engine.engine_matrix(X)
     engs = []
     for r in range(W):
         Xl = X[offs[r] : offs[r] + sizes[r]].contiguous()
         nl = norms[offs[r] : offs[r] + sizes[r]].contiguous()
-        e = engine.ShardEngine(Xl, nl, k, shard_offset=offs[r], world_size=W, mode=mode)
+        e = engine.ShardEngine(Xl, nl, k, shard_offset=offs[r], world_size=W, mode=mode, element_order=element_order)
         e.init_state()
         engs.append(e)
 
