@@ -60,7 +60,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the c2 / c4 / c5 legs")
     ap.add_argument("--configs", default="c2,c4,c5", help="which of the other configurations to run")
-    ap.add_argument("--c5-rows", type=int, default=0, help="accretion leg: anchors = candidates = this many rows (0 = 50M)")
+    ap.add_argument("--c5-rows", type=int, default=0, help="accretion leg: anchors = candidates = this many rows (0 = 50M from 4 GPUs on, the pinned 5M case below)")
     ap.add_argument("--c5-max-k", type=int, default=14)
     ap.add_argument("--cpu-rows", type=int, default=32_000_000, help="rows of the CPU reference's sample")
     ap.add_argument("--no-ref-cuda", action="store_true", help="reference arm: skip the reference's own CUDA fps")
@@ -731,6 +731,11 @@ def run_accretion_config(args, world, rank, device):
     reference's own list is committed (its run at full size costs more GPU time than a round has)."""
     if world < 2:
         return {"skipped": "the accretion configuration is quoted on 2, 4 and 8 GPUs"}
+    if world < 4 and not args.c5_rows:
+        # 50 M rows per GPU: several minutes of wall clock for this leg alone; --c5-rows 50000000 runs it
+        out = {"skipped": "the full-size run takes part from 4 GPUs on (4 GPUs: 249 s); --c5-rows forces it"}
+        out["pinned_case"] = accretion_case(5_000_000, 12, world, rank, device)
+        return out
     out = accretion_case(args.c5_rows or 50_000_000, args.c5_max_k, world, rank, device)
     torch.cuda.empty_cache()
     if out["parity"]["equal"] is None:
