@@ -34,6 +34,7 @@
 #include "step_plain.cuh"
 #include "step_queue.cuh"
 #include "step_tma.cuh"
+#include "step_tma_half.cuh"
 #include "step_lanes.cuh"
 #include "small_kernels.cuh"
 #include "select.cuh"
@@ -172,6 +173,26 @@ int launch_step_tma(const cs_state* s, cudaStream_t st, const DevInfo& dv) {
     int64_t cap = (int64_t)sms * B;                         // resident blocks, each with its own ring
     int grid = (int)(ntiles < 1 ? 1 : (ntiles < cap ? ntiles : cap));
     fps_step_tma_kernel<CPL, S, HALF, W, B><<<grid, (W + 1) * 32, smem, st>>>(*s, tile_rows);
+    return check_launch();
+}
+
+// dense mode over half rows: J elements per lane, RB rows reduced together
+template <int J, int RB, int S, int B, int T, int W>
+int launch_step_tma_half(const cs_state* s, cudaStream_t st, const DevInfo& dv) {
+    static_assert(W <= kTmaMaxWarps && (W % 8) == 0 && 32 % RB == 0, "consumer warps / batch");
+    const int D = s->D;
+    int tile_rows = T / (D * 2);
+    tile_rows = tile_rows > 32 * W ? 32 * W : tile_rows;
+    tile_rows -= tile_rows % (W * RB);                     // a warp's share of a tile is whole batches
+    if (tile_rows < W * RB) tile_rows = W * RB;
+    const size_t smem = (size_t)S * tile_rows * (D * 2 + 12);
+    static thread_local KernelTune tune;
+    const int rc = tune_kernel(fps_step_tma_half_kernel<J, RB, S, W, B>, tune, dv.dev, smem, (W + 1) * 32, nullptr);
+    if (rc) return rc;
+    const int64_t ntiles = (s->N_local + tile_rows - 1) / tile_rows;
+    const int64_t cap = (int64_t)dv.sms * B;
+    const int grid = (int)(ntiles < 1 ? 1 : (ntiles < cap ? ntiles : cap));
+    fps_step_tma_half_kernel<J, RB, S, W, B><<<grid, (W + 1) * 32, smem, st>>>(*s, tile_rows);
     return check_launch();
 }
 
@@ -359,6 +380,14 @@ int cs_fps_step(const cs_state* s, uint32_t mode, cs_stream stream) {
         if (D <= 256) return launch_step_tma<2, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d);
         if (D <= 512) return launch_step_tma<4, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d);
         return launch_step_tma<8, false, kRingWide.stages, kRingWide.blocks, kRingWide.tile_bytes, kRingWide.warps>(s, st, d);
+    }
+    if (mode == CS_MODE_DENSE && bulk_ok && (s->flags & CS_F_X_HALF) && (D & 7) == 0 && D <= 1024 && s->N_local > 0) {
+        if (D <= 32) return launch_step_tma_half<1, 8, 5, 1, 65536, 16>(s, st, d);
+        if (D <= 64) return launch_step_tma_half<2, 8, 3, 1, 65536, 16>(s, st, d);
+        if (D <= 128) return launch_step_tma_half<4, 8, 3, 1, 65536, 16>(s, st, d);
+        if (D <= 256) return launch_step_tma_half<8, 8, 5, 1, 40960, 8>(s, st, d);
+        if (D <= 512) return launch_step_tma_half<16, 4, 5, 1, 40960, 8>(s, st, d);
+        return launch_step_tma_half<32, 2, 5, 1, 40960, 8>(s, st, d);
     }
     const bool generic = element_order || (D & 3) != 0 || D > 1024;
     if (generic && mode == CS_MODE_PRUNE && s->N_local > 0 && D <= 16384) return launch_step_queue<0, false>(s, st, d);

@@ -107,6 +107,8 @@ _CELLS_MIN_ROWS = 1 << 18        # CELLS_MIN_ROWS: below this a full scan costs 
 _CELLS_PROBE_PICKS = 32          # CELLS_PROBE_PICKS: picks after a build before the visited share is read back
 _CELLS_GIVE_UP_SHARE = 0.2       # CELLS_GIVE_UP_SHARE: above this share of the slots per pick the scan kernel wins
 _CELLS_LIVE_GATE = 0.1           # CELLS_LIVE_GATE: no index while a pick still evaluates this share of the rows
+_HALF_RING_SHARE = 0.12         # HALF_RING_SHARE: float16 rows stay on the bulk-copy ring (2 bytes per element, every row)
+                                 # while a pick still evaluates this share of them; 0 = never
 _EARLY_DENSE_PICKS = 24          # EARLY_DENSE_PICKS: nearly every row passes the triangle test this early, so
                                  # X is streamed with the bulk-copy ring
 
@@ -185,6 +187,14 @@ class ShardEngine:
         self._give_up_share = _knob("CELLS_GIVE_UP_SHARE", _CELLS_GIVE_UP_SHARE, float)
         self._early_dense = max(0, _knob("EARLY_DENSE_PICKS", _EARLY_DENSE_PICKS))
         self._live_gate = _knob("CELLS_LIVE_GATE", _CELLS_LIVE_GATE, float)
+        # float16 rows in whole 16-byte units: dense picks stream them through the bulk-copy ring at
+        # HBM speed, pruned picks gather them with 2-byte loads
+        self._ring_share = _knob("HALF_RING_SHARE", _HALF_RING_SHARE, float)
+        self.half_ring = bool(self.half_rows and self.on_cuda and self.mode == MODE_PRUNE and self._ring_share > 0
+                              and self.D % 8 == 0 and self.D <= 1024
+                              and self.N_local >= _knob("CELLS_MIN_ROWS", _CELLS_MIN_ROWS))
+        self._ring_until = 0                   # picks below this count take the ring
+        self._ring_off = False                 # the evaluated share fell below the threshold
         self.cells_enabled = bool(
             cells and self.on_cuda and _cells_env() and self.mode == MODE_PRUNE and not self.element_order
             and self.D % 4 == 0 and self.D <= 1024 and self.cap <= 65536
@@ -263,12 +273,14 @@ class ShardEngine:
         self.native.init_state(self.state, self._stream())
         self.n_host = 0
         self._cells_ok = False
+        self._ring_until, self._ring_off = 0, False
 
     def reset_ctl(self, n_sel: int) -> None:
         self.native.reset_ctl(self.state, int(n_sel), self._stream())
         self.n_host = int(n_sel)
         self._cells_ok = False
         self._cells_scan_until = 0
+        self._ring_until, self._ring_off = 0, False
 
     def _before_publish(self) -> None:
         # peer exchange: sequence s+1 may only be published once every peer's s has been seen
@@ -466,6 +478,21 @@ class ShardEngine:
         n = int(n)
         if n <= 0:
             return
+        if self.half_ring and rules == RULE_NONE and self.n_host is not None and not self._ring_off:
+            # float16 rows: the ring while most rows are still evaluated (one read-back per stretch
+            # of picks: 24, then every 25 % more), the pruned scan for the rest of the run
+            while n > 0 and not self._ring_off:
+                cur = self.n_host
+                if cur >= max(self._ring_until, self._early_dense):
+                    if cur > 0 and self.read_ctl().live_rows <= self._ring_share * self.N_local:
+                        self._ring_off = True
+                        break
+                    self._ring_until = max(cur + 16, int(cur * 1.25))
+                m = min(n, max(self._ring_until, self._early_dense) - cur)
+                self._replay(m, rules, MODE_DENSE)
+                n -= m
+            if n <= 0:
+                return
         if not self._uses_cells(rules):
             self._replay(n, rules, None)
             return

@@ -99,7 +99,8 @@ typedef struct cs_ctl_view {
     int32_t viable;      /* simulation: 1 once separation beat coverage                       */
     float sep;           /* simulation: running min of the pick values                        */
     int32_t steps;       /* simulation: picks committed since cs_sim_begin                    */
-    uint64_t live_rows;  /* rows whose distance the last cs_fps_step evaluated               */
+    uint64_t live_rows;  /* rows whose distance the last cs_fps_step evaluated (dense mode over
+                            half rows: rows the pruned scan would have evaluated)             */
     float last_val;      /* value (max h) of the last committed pick                          */
     int32_t last_idx;    /* global index of the last committed pick (-1: nothing left)       */
     uint32_t xseq;       /* peer exchange: sequence number of the last published candidate   */

@@ -120,11 +120,15 @@ def test_float16_and_float64_inputs(dtype, N, D, k, mode):
     assert_matches_oracle(eng, X, norms, k)
 
 
-@pytest.mark.parametrize("N,D,k", [(3000, 128, 200), (1501, 50, 64), (2000, 7, 100), (600, 1028, 40), (777, 1, 30)])
+@pytest.mark.parametrize("N,D,k", [(3000, 128, 200), (1501, 50, 64), (2000, 7, 100), (600, 1028, 40), (777, 1, 30),
+                                   # dense mode: the bulk-copy ring over half rows, every width bucket and ragged last tiles
+                                   (4099, 8, 60), (5001, 32, 80), (2050, 64, 64), (1501, 72, 64), (3003, 200, 50),
+                                   (1290, 256, 64), (777, 512, 40), (530, 520, 30), (431, 1024, 40), (40000, 128, 64), (3, 16, 3)])
 @pytest.mark.parametrize("mode", [MODE_PRUNE, MODE_DENSE])
 def test_half_rows_read_in_place_equal_the_converted_matrix(N, D, k, mode, monkeypatch):
     """float16 rows on the device are read where they lie (CS_F_X_HALF), odd row widths and
-    therefore 2-byte aligned rows included; same bits as the run over a float32 copy."""
+    therefore 2-byte aligned rows included; same bits as the run over a float32 copy.  Dense mode
+    with rows of whole 16-byte units streams them through the bulk-copy ring (fps_step_tma_half_kernel)."""
     from tests.data import as_dtype
     X = as_dtype(gaussian_mixture(N, D, 8, seed=N + D), "float16")
     a, norms = run_engine(X, k, mode=mode)
@@ -138,13 +142,34 @@ def test_half_rows_read_in_place_equal_the_converted_matrix(N, D, k, mode, monke
     assert_matches_oracle(a, X, norms, k)
 
 
+@pytest.mark.parametrize("N,D,k,share", [(6000, 64, 600, 0.12), (5000, 128, 300, 0.5), (3000, 256, 200, 0.02)])
+def test_half_rows_leave_the_ring_for_the_pruned_scan(N, D, k, share, monkeypatch):
+    """Product mode over float16 rows: the bulk-copy ring while a pick still evaluates a large
+    share of the rows, then the pruned scan; the switch (a host decision between picks) changes no bit."""
+    from tests.data import as_dtype
+    monkeypatch.setenv("CORESETS_B200_CELLS_MIN_ROWS", "1")
+    monkeypatch.setenv("CORESETS_B200_EARLY_DENSE_PICKS", "3")
+    monkeypatch.setenv("CORESETS_B200_HALF_RING_SHARE", str(share))
+    X = as_dtype(gaussian_mixture(N, D, 8, seed=N + D), "float16")
+    eng, norms = run_engine(X, k)
+    assert eng.half_ring and eng._ring_until > 3          # some stretches ran on the ring ...
+    if share >= 0.5:
+        assert eng._ring_off                              # ... and the scan took over
+    assert_matches_oracle(eng, X, norms, k)
+    monkeypatch.setenv("CORESETS_B200_HALF_RING_SHARE", "0")
+    plain, _ = run_engine(X, k)
+    assert not plain.half_ring
+    assert torch.equal(plain.selected, eng.selected) and torch.equal(plain.h.view(torch.int32), eng.h.view(torch.int32))
+
+
 @pytest.mark.parametrize("sizes,D", [([1000, 1003], 64), ([0, 700, 0, 650], 50), ([301, 299, 2, 300], 129)])
-def test_half_rows_multi_rank_kernels_on_one_device(sizes, D):
+@pytest.mark.parametrize("mode", [MODE_PRUNE, MODE_DENSE])
+def test_half_rows_multi_rank_kernels_on_one_device(sizes, D, mode):
     """Half rows with world_size > 1: the candidate row travels widened to float32 (multi.cu:245)."""
     from tests.data import as_dtype
     N, k = sum(sizes), 100
     X = as_dtype(with_duplicates(gaussian_mixture(N, D, 8, seed=N + D), 20, seed=2), "float16")
-    engs, norms, offs = _emulate_ranks(X, sizes, k, first=3)
+    engs, norms, offs = _emulate_ranks(X, sizes, k, first=3, mode=mode)
     assert all(e.half_rows for e in engs)
     with oracle.element_order():
         o_sel, o_eps, o_h, o_v = oracle.fps_sharded(X.astype(np.float32), norms, k, sizes, first=3)
@@ -458,15 +483,18 @@ def test_peer_exchange_kernels_on_one_device(sizes, monkeypatch):
         np.testing.assert_array_equal(bits(e.h[:n].cpu().numpy()), bits(o_h[offs[r] : offs[r] + n]))
 
 
-def test_dense_pipe_wait_times_out_with_a_status(monkeypatch):
-    """The bulk-copy ring of dense mode with a producer that starts no copy (test hook): the
-    consumers' bounded mbarrier wait gives up, the status word says so, nothing faults and the
-    context stays usable."""
+@pytest.mark.parametrize("half_rows", [False, True])
+def test_dense_pipe_wait_times_out_with_a_status(half_rows, monkeypatch):
+    """The bulk-copy ring of dense mode (float32 rows, half rows) with a producer that starts no
+    copy (test hook): the consumers' bounded mbarrier wait gives up, the status word says so,
+    nothing faults and the context stays usable."""
     from coresets_b200._native import F_TEST_STALL_PIPE
     monkeypatch.setenv("CORESETS_B200_XCHG_TIMEOUT_MS", "40")
     dev = torch.device("cuda:0")
     X = torch.from_numpy(gaussian_mixture(5000, 128, 4, seed=1)).to(dev)
-    eng = engine.ShardEngine(X, engine.row_norms(X), 8, mode=MODE_DENSE)
+    if half_rows:
+        X = X.to(torch.float16)
+    eng = engine.ShardEngine(X, engine.row_norms(X), 8, mode=MODE_DENSE, element_order=half_rows)
     eng._extra_flags = F_TEST_STALL_PIPE
     eng.state = eng._make_state()
     eng.init_state()
