@@ -3,6 +3,7 @@
     python -m coresets_b200.profile_cases cells <workload> <rows> <k>   fps_cuda to k picks, single launches
                                                                          (no CUDA graphs): cell-index kernels
     python -m coresets_b200.profile_cases dense <workload> <rows>       six dense picks: the bulk-copy kernel
+    python -m coresets_b200.profile_cases dense16 <workload> <rows>     the same over float16 rows
 
 Rows are the first <rows> of the named synthetic workload (coresets_b200/synth.py), generated on
 the device.
@@ -29,8 +30,10 @@ def main(argv) -> None:
         sel = fps_cuda(X, k)
         torch.cuda.synchronize()
         print("done", wname, rows, k, sel[-3:].tolist())
-    elif what == "dense":
-        eng = engine.ShardEngine(X, engine.row_norms(X), k, mode=MODE_DENSE)
+    elif what in ("dense", "dense16"):
+        if what == "dense16":
+            X = X.to(torch.float16)
+        eng = engine.ShardEngine(X, engine.row_norms(X), k, mode=MODE_DENSE, element_order=what == "dense16")
         eng.init_state()
         eng.pick_forced(0)
         for _ in range(6):
