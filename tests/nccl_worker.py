@@ -38,6 +38,9 @@ def main() -> None:
     for case in cfg["cases"]:
         N, D, k, seed = case["N"], case["D"], case["k"], case.get("seed")
         X_np = with_duplicates(gaussian_mixture(N, D, 8, seed=N + D), 30, seed=2)
+        other_dtype = case.get("dtype", "float32") != "float32"      # float16: summed element-wise, rows read in place
+        if other_dtype:
+            X_np = X_np.astype(case["dtype"])
         sizes = case["sizes"]
         offs = [sum(sizes[:r]) for r in range(world)]
         X_local = torch.from_numpy(np.ascontiguousarray(X_np[offs[rank] : offs[rank] + sizes[rank]])).to(dev)
@@ -46,7 +49,8 @@ def main() -> None:
         norms = np.concatenate([
             engine.row_norms(torch.from_numpy(np.ascontiguousarray(X_np[offs[r] : offs[r] + sizes[r]])).to(dev)).cpu().numpy()
             if sizes[r] > 0 else np.zeros(0, np.float32) for r in range(world)])
-        o_sel, o_eps, _, _ = oracle.fps_sharded(X_np, norms, k, sizes, first=seed or 0)
+        with oracle.element_order(other_dtype):
+            o_sel, o_eps, _, _ = oracle.fps_sharded(X_np.astype(np.float32), norms, k, sizes, first=seed or 0)
         if not np.array_equal(sel.cpu().numpy(), o_sel):
             failures.append(f"{case}: selected differs from the oracle on rank {rank}")
         if not np.array_equal(eps.numpy().view(np.int32), o_eps.view(np.int32)):

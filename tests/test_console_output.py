@@ -44,16 +44,13 @@ import pytest
 @pytest.mark.parametrize("case,knobs,golden,profile", [(CASE, None, "verbose_sharded.txt", True),
                                                        (CASE_KNOBS, KNOBS, "verbose_sharded_knobs.txt", False)])
 def test_sharded_driver_console_output(monkeypatch, case, knobs, golden, profile):
-    import socket
     import torch.distributed as dist
+    from tests.ports import free_port
     sh = importlib.import_module("coresets_b200.cuda.multi.sharded")
     monkeypatch.setattr(sh, "_REQUIRE_CUDA", False)
     c, X, order = _setup(monkeypatch, case, knobs)
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        port = s.getsockname()[1]
     monkeypatch.setenv("MASTER_ADDR", "127.0.0.1")
-    monkeypatch.setenv("MASTER_PORT", str(port))
+    monkeypatch.setenv("MASTER_PORT", str(free_port()))
     dist.init_process_group("gloo", rank=0, world_size=1)
     try:
         buf = io.StringIO()

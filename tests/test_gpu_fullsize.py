@@ -9,7 +9,6 @@ single one when the rows fit its memory.
 """
 import json
 import os
-import socket
 import subprocess
 import sys
 from pathlib import Path
@@ -18,22 +17,22 @@ import numpy as np
 import pytest
 import torch
 
+from tests.ports import address_in_use, free_port
+
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 GOLDEN = ROOT / "tests" / "golden"
 
 
-def _free_port() -> int:
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
-
-
 def _run(script: str, args, world: int, timeout: int, extra_env=None):
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(ROOT / "tests" / "golden" / script), *args]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, cwd=str(ROOT), env=env)
+    for attempt in range(3):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", str(free_port()), str(ROOT / "tests" / "golden" / script), *args]
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, cwd=str(ROOT), env=env)
+        if res.returncode != 0 and address_in_use([res.stdout, res.stderr]) and attempt < 2:
+            continue                                   # the rendezvous port was taken: another one
+        break
     assert res.returncode == 0, (res.stdout + res.stderr)[-3000:]
     return res.stdout
 

@@ -2,43 +2,42 @@
 reference's sharded driver.  With one visible GPU only the world_size = 1 group is exercised."""
 import json
 import os
-import time
-import socket
 import subprocess
+import time
 import sys
 from pathlib import Path
 
 import pytest
 import torch
 
+from tests.ports import address_in_use, free_port
+
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def _free_port() -> int:
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
-
-
 def _launch(world: int, cfg: dict, timeout: int = 420, extra_env=None) -> None:
-    port = _free_port()
-    procs = []
-    for r in range(world):
-        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r),
-                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", **(extra_env or {}))
-        procs.append(subprocess.Popen([sys.executable, str(ROOT / "tests" / "nccl_worker.py"), json.dumps(cfg)],
-                                      env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
-    outs = []
-    deadline = time.time() + timeout
-    for p in procs:
-        try:
-            o, _ = p.communicate(timeout=max(1.0, deadline - time.time()))
-        except subprocess.TimeoutExpired:
-            p.kill()
-            o, _ = p.communicate()
-            o = (o or "") + "\n[killed after timeout]"
-        outs.append(o)
+    for attempt in range(3):
+        port = free_port()
+        procs = []
+        for r in range(world):
+            env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r),
+                       MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", **(extra_env or {}))
+            procs.append(subprocess.Popen([sys.executable, str(ROOT / "tests" / "nccl_worker.py"), json.dumps(cfg)],
+                                          env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+        outs = []
+        deadline = time.time() + timeout
+        for p in procs:
+            try:
+                o, _ = p.communicate(timeout=max(1.0, deadline - time.time()))
+            except subprocess.TimeoutExpired:
+                p.kill()
+                o, _ = p.communicate()
+                o = (o or "") + "\n[killed after timeout]"
+            outs.append(o)
+        if any(p.returncode != 0 for p in procs) and address_in_use(outs) and attempt < 2:
+            continue                                   # the rendezvous port was taken: another one
+        break
     for r, p in enumerate(procs):
         assert p.returncode == 0, f"rank {r} failed:\n{outs[r][-3000:]}"
     for r in range(world):
@@ -58,6 +57,9 @@ def _cases(world: int):
         dict(N=6000, D=64, k=200, sizes=split(6000), seed=4321),   # seeded first pick
         dict(N=5001, D=256, k=96, sizes=split(5001, empty=True)),  # an empty shard when world > 1
         dict(N=3000, D=50, k=64, sizes=split(3000)),               # D % 4 != 0
+        # float16 rows read in place; with the eager knobs below each rank leaves the dense ring for
+        # the pruned scan at its own pick count
+        dict(N=8000, D=64, k=400, sizes=split(8000), dtype="float16"),
     ]
 
 

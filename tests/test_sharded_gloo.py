@@ -2,7 +2,6 @@
 library, compared with the oracle's emulation of the reference's sharded driver."""
 import json
 import os
-import socket
 import subprocess
 import sys
 from pathlib import Path
@@ -12,33 +11,32 @@ import pytest
 
 import oracle
 from tests.data import clustered_jitter, with_duplicates
+from tests.ports import address_in_use, free_port
 
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def _free_port() -> int:
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
-
-
 def _run(world: int, cfg: dict, timeout: int = 240) -> None:
-    port = _free_port()
-    procs = []
-    for r in range(world):
-        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r),
-                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), OMP_NUM_THREADS="1")
-        procs.append(subprocess.Popen([sys.executable, str(ROOT / "tests" / "gloo_worker.py"), json.dumps(cfg)],
-                                      env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
-    outs = []
-    try:
-        for p in procs:
-            o, _ = p.communicate(timeout=timeout)
-            outs.append(o)
-    finally:
-        for p in procs:
-            if p.poll() is None:
-                p.kill()
+    for attempt in range(3):
+        port = free_port()
+        procs = []
+        for r in range(world):
+            env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r),
+                       MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), OMP_NUM_THREADS="1")
+            procs.append(subprocess.Popen([sys.executable, str(ROOT / "tests" / "gloo_worker.py"), json.dumps(cfg)],
+                                          env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+        outs = []
+        try:
+            for p in procs:
+                o, _ = p.communicate(timeout=timeout)
+                outs.append(o)
+        finally:
+            for p in procs:
+                if p.poll() is None:
+                    p.kill()
+        if any(p.returncode != 0 for p in procs) and address_in_use(outs) and attempt < 2:
+            continue                                   # the rendezvous port was taken: another one
+        break
     for r, p in enumerate(procs):
         assert p.returncode == 0, f"rank {r} failed:\n{outs[r][-3000:]}"
 

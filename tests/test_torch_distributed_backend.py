@@ -2,12 +2,13 @@
 two-rank gloo group against the lists the reference's own `accrete_distributed` produced
 (tests/golden/torch_accrete.npz, keys `<case>_dist`; tests/golden/make_golden_torch_accrete.py)."""
 import os
-import socket
 import subprocess
 import sys
 from pathlib import Path
 
 import numpy as np
+
+from tests.ports import address_in_use, free_port
 
 ROOT = Path(__file__).resolve().parent.parent
 WORKER = '''
@@ -30,14 +31,16 @@ dist.destroy_process_group()
 
 def test_distributed_torch_accrete_reproduces_the_reference(tmp_path):
     from tests.golden.make_golden_torch_accrete import CASES
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        port = s.getsockname()[1]
     code = WORKER.format(root=str(ROOT), out=str(tmp_path))
-    procs = [subprocess.Popen([sys.executable, "-c", code],
-                              env=dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port)),
-                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
-    outs = [p.communicate(timeout=600)[0] for p in procs]
+    for attempt in range(3):
+        port = free_port()
+        procs = [subprocess.Popen([sys.executable, "-c", code],
+                                  env=dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port)),
+                                  stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+        outs = [p.communicate(timeout=600)[0] for p in procs]
+        if any(p.returncode != 0 for p in procs) and address_in_use(outs) and attempt < 2:
+            continue                                   # the rendezvous port was taken: another one
+        break
     for r, p in enumerate(procs):
         assert p.returncode == 0, outs[r][-2000:]
     z = np.load(ROOT / "tests" / "golden" / "torch_accrete.npz")
