@@ -54,7 +54,9 @@ extern "C" {
 #define CS_MODE_PRUNE_INLINE 2u /* prune mode evaluating each remaining row where the scan meets it */
 #define CS_MODE_DENSE 1u   /* every live row's distance is computed; the bound only masks the
                               update, so results are identical to CS_MODE_PRUNE; X is streamed by
-                              bulk asynchronous (TMA) copies when D % 4 == 0 and 32 <= D <= 1024 */
+                              bulk asynchronous (TMA) copies when D % 4 == 0 and 32 <= D <= 1024
+                              (half rows, CS_F_X_HALF: D % 8 == 0 and D <= 1024), X / h / voronoi /
+                              norms 16-byte aligned */
 #define CS_MODE_DENSE_LDG 3u /* dense mode with plain 128-bit loads (the path other row widths take) */
 /* cs_state.flags */
 #define CS_F_ELEMENT_ORDER 1u /* every dot product sums element-wise (lane l takes elements l, l+32,
