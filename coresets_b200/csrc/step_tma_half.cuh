@@ -52,6 +52,60 @@ __device__ __forceinline__ int tree_lane_of(const int r) {
     return ((r & 1) << 4) | (((r >> 1) & 1) << 3) | (((r >> 2) & 1) << 2);
 }
 
+// d = a * b + c with a and b IEEE halves, rounded once: what __fmaf_rn gives for the widened
+// values, without the two conversions.  (No flush-to-zero form exists and none is needed: products
+// of halves are multiples of 2^-48, so are all their partial sums, and no subnormal float can appear.)
+__device__ __forceinline__ float fma_half(const __half a, const __half b, float c) {
+    asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(c) : "h"(__half_as_ushort(a)), "h"(__half_as_ushort(b)));
+    return c;
+}
+
+// Sums of RB rows against the centre: rows_h points at element `lane` of the batch's first row.
+// FULL: D == 32 J, no lane is ever out of the row.  MIXED: the centre is exactly representable in
+// half (it is whenever it was committed from half rows) and the fma takes both operands as halves;
+// otherwise the float centre is re-read from global memory (`cen`, the centre's row of X_sel).
+template <int J, int RB, bool FULL, bool MIXED>
+__device__ __forceinline__ float batch_rows(const __half* __restrict__ rows_h, const int D, const float* __restrict__ cen,
+                                            const __half (&cenh)[J], const int lane) {
+    float acc[RB];
+#pragma unroll
+    for (int b = 0; b < RB; ++b) acc[b] = 0.0f;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+        if (FULL || lane + 32 * j < D) {
+            __half x[RB];
+#pragma unroll
+            for (int b = 0; b < RB; ++b) x[b] = rows_h[(size_t)b * D + 32 * j];
+#pragma unroll
+            for (int b = 0; b < RB; ++b)
+                acc[b] = MIXED ? fma_half(x[b], cenh[j], acc[b]) : __fmaf_rn(__half2float(x[b]), __ldg(cen + lane + 32 * j), acc[b]);
+        }
+    }
+    return tree_rows<RB>(acc, lane);
+}
+
+// Wide rows (J > 8): the float centre stays in registers and every element is widened -- a second
+// copy of the centre as halves, or a re-read per element, costs more than the conversions
+// (2 M x 1024: 0.61 ms this way, 0.80 ms with the half centre spilling out of 96 registers).
+template <int J, int RB>
+__device__ __forceinline__ float batch_rows_wide(const __half* __restrict__ rows_h, const int D, const float (&cen)[J],
+                                                 const int lane) {
+    float acc[RB];
+#pragma unroll
+    for (int b = 0; b < RB; ++b) acc[b] = 0.0f;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+        if (lane + 32 * j < D) {
+            __half x[RB];
+#pragma unroll
+            for (int b = 0; b < RB; ++b) x[b] = rows_h[(size_t)b * D + 32 * j];
+#pragma unroll
+            for (int b = 0; b < RB; ++b) acc[b] = __fmaf_rn(__half2float(x[b]), cen[j], acc[b]);
+        }
+    }
+    return tree_rows<RB>(acc, lane);
+}
+
 // J = elements per lane (D <= 32 J), RB = rows reduced together (rows of a tile per consumer warp is a
 // multiple of RB, at most 32), S stages, W consumer warps, B blocks per SM.
 template <int J, int RB, int S, int W, int B>
@@ -132,12 +186,28 @@ __global__ void __launch_bounds__((W + 1) * 32, B) fps_step_tma_half_kernel(cons
         }
     } else {
         // ---- consumers ------------------------------------------------------------------------------
-        float cen[J];
-        {
-            const float* c = s.X_sel + (int64_t)i * D;
+        constexpr bool kNarrow = J <= 8;                     // see batch_rows_wide
+        constexpr int JH = kNarrow ? J : 1, JF = kNarrow ? 1 : J;
+        const float* cen = s.X_sel + (int64_t)i * D;
+        __half cenh[JH];
+        float cenf[JF];
+        bool exact = true;
+        if constexpr (kNarrow) {
 #pragma unroll
-            for (int j = 0; j < J; ++j) cen[j] = (lane + 32 * j < D) ? c[lane + 32 * j] : 0.0f;
+            for (int j = 0; j < J; ++j) {
+                const float c = (lane + 32 * j < D) ? cen[lane + 32 * j] : 0.0f;
+                cenh[j] = __float2half_rn(c);
+                exact = exact && (__half2float(cenh[j]) == c);
+            }
+            cenf[0] = 0.0f;
+        } else {
+#pragma unroll
+            for (int j = 0; j < J; ++j) cenf[j] = (lane + 32 * j < D) ? cen[lane + 32 * j] : 0.0f;
+            cenh[0] = __float2half_rn(0.0f);
         }
+        // the same centre in every warp of every block: one verdict for the whole launch
+        const bool mixed = __all_sync(kFull, exact);
+        const bool full = (D == 32 * J);
         int n = 0;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++n) {
             const int q = n % S;
@@ -170,20 +240,15 @@ __global__ void __launch_bounds__((W + 1) * 32, B) fps_step_tma_half_kernel(cons
             // and never used.
             for (int base = 0; base < rpw; base += RB) {
                 if (((m >> base) & ((1u << RB) - 1u)) == 0u) continue;
-                float acc[RB];
-#pragma unroll
-                for (int b = 0; b < RB; ++b) acc[b] = 0.0f;
-#pragma unroll
-                for (int j = 0; j < J; ++j) {
-                    if (lane + 32 * j < D) {
-                        __half x[RB];
-#pragma unroll
-                        for (int b = 0; b < RB; ++b) x[b] = rows_h[(size_t)(base + b) * D + 32 * j];
-#pragma unroll
-                        for (int b = 0; b < RB; ++b) acc[b] = __fmaf_rn(__half2float(x[b]), cen[j], acc[b]);
-                    }
+                const __half* bh = rows_h + (size_t)base * D;
+                float v;
+                if constexpr (kNarrow) {
+                    if (!mixed) v = batch_rows<J, RB, false, false>(bh, D, cen, cenh, lane);
+                    else if (full) v = batch_rows<J, RB, true, true>(bh, D, cen, cenh, lane);
+                    else v = batch_rows<J, RB, false, true>(bh, D, cen, cenh, lane);
+                } else {
+                    v = batch_rows_wide<J, RB>(bh, D, cenf, lane);
                 }
-                const float v = tree_rows<RB>(acc, lane);
                 const int r = lane - base;
                 const float mine = __shfl_sync(kFull, v, tree_lane_of<RB>(r & (RB - 1)));
                 if (r >= 0 && r < RB) mydot = mine;

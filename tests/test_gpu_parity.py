@@ -142,6 +142,33 @@ def test_half_rows_read_in_place_equal_the_converted_matrix(N, D, k, mode, monke
     assert_matches_oracle(a, X, norms, k)
 
 
+@pytest.mark.parametrize("D", [128, 72, 1024])
+def test_half_ring_with_a_centre_that_is_no_half(D):
+    """The half-row dense kernel multiplies halves directly when the centre is representable in
+    half (always, when it was committed from half rows); a centre table written otherwise takes the
+    widening path.  Both against the float32 kernels on the same perturbed centre."""
+    from tests.data import as_dtype
+    N = 3000
+    Xh = torch.from_numpy(as_dtype(gaussian_mixture(N, D, 8, seed=N + D), "float16")).cuda()
+    norms = engine.row_norms(Xh)
+    engs = []
+    for X in (Xh, Xh.to(torch.float32)):
+        e = engine.ShardEngine(X, norms, 8, mode=MODE_DENSE, element_order=True)
+        e.init_state()
+        e.force_pick(5)
+        for i in range(6):
+            e.commit()
+            if i % 2 == 1:
+                e.X_sel[i, ::3] += 1.0e-5          # not a half any more
+            e.step()
+        e.check_status()
+        engs.append(e)
+    a, b = engs
+    assert a.half_rows and not b.half_rows
+    assert torch.equal(a.h.view(torch.int32), b.h.view(torch.int32)) and torch.equal(a.voronoi, b.voronoi)
+    assert torch.equal(a.selected[:6], b.selected[:6])
+
+
 @pytest.mark.parametrize("N,D,k,share", [(6000, 64, 600, 0.12), (5000, 128, 300, 0.5), (3000, 256, 200, 0.02)])
 def test_half_rows_leave_the_ring_for_the_pruned_scan(N, D, k, share, monkeypatch):
     """Product mode over float16 rows: the bulk-copy ring while a pick still evaluates a large
