@@ -60,6 +60,14 @@ __device__ __forceinline__ float fma_half(const __half a, const __half b, float 
     return c;
 }
 
+// One half from shared memory, by its shared-window address (an explicit ld.shared: the rows reach
+// these functions through pointers whose address space the compiler need not know).
+__device__ __forceinline__ __half lds_half(const uint32_t addr) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return __ushort_as_half(v);
+}
+
 // Sums of RB rows against the centre: rows_h points at element `lane` of the batch's first row.
 // FULL: D == 32 J, no lane is ever out of the row.  MIXED: the centre is exactly representable in
 // half (it is whenever it was committed from half rows) and the fma takes both operands as halves;
@@ -68,6 +76,7 @@ template <int J, int RB, bool FULL, bool MIXED>
 __device__ __forceinline__ float batch_rows(const __half* __restrict__ rows_h, const int D, const float* __restrict__ cen,
                                             const __half (&cenh)[J], const int lane) {
     float acc[RB];
+    const uint32_t a0 = smem_u32(rows_h), row_bytes = 2u * (uint32_t)D;
 #pragma unroll
     for (int b = 0; b < RB; ++b) acc[b] = 0.0f;
 #pragma unroll
@@ -75,7 +84,7 @@ __device__ __forceinline__ float batch_rows(const __half* __restrict__ rows_h, c
         if (FULL || lane + 32 * j < D) {
             __half x[RB];
 #pragma unroll
-            for (int b = 0; b < RB; ++b) x[b] = rows_h[(size_t)b * D + 32 * j];
+            for (int b = 0; b < RB; ++b) x[b] = lds_half(a0 + (uint32_t)b * row_bytes + 64u * j);
 #pragma unroll
             for (int b = 0; b < RB; ++b)
                 acc[b] = MIXED ? fma_half(x[b], cenh[j], acc[b]) : __fmaf_rn(__half2float(x[b]), __ldg(cen + lane + 32 * j), acc[b]);
@@ -91,6 +100,7 @@ template <int J, int RB>
 __device__ __forceinline__ float batch_rows_wide(const __half* __restrict__ rows_h, const int D, const float (&cen)[J],
                                                  const int lane) {
     float acc[RB];
+    const uint32_t a0 = smem_u32(rows_h), row_bytes = 2u * (uint32_t)D;
 #pragma unroll
     for (int b = 0; b < RB; ++b) acc[b] = 0.0f;
 #pragma unroll
@@ -98,7 +108,7 @@ __device__ __forceinline__ float batch_rows_wide(const __half* __restrict__ rows
         if (lane + 32 * j < D) {
             __half x[RB];
 #pragma unroll
-            for (int b = 0; b < RB; ++b) x[b] = rows_h[(size_t)b * D + 32 * j];
+            for (int b = 0; b < RB; ++b) x[b] = lds_half(a0 + (uint32_t)b * row_bytes + 64u * j);
 #pragma unroll
             for (int b = 0; b < RB; ++b) acc[b] = __fmaf_rn(__half2float(x[b]), cen[j], acc[b]);
         }
