@@ -112,14 +112,23 @@ __global__ void __launch_bounds__(kThreads, CPL == 0 ? 2 : CS_MIN_BLOCKS) fps_st
 #pragma unroll
                     for (int b = 0; b < 4; ++b) acc[b] = __fadd_rn(acc[b], chunk_dot(a[b], cc));
                 }
+            } else if (half_rows) {
+                const __half* Xh = reinterpret_cast<const __half*>(s.X);
+#pragma unroll 4
+                for (int c = lane; c < D; c += 32) {                 // _shared.cuh:52-58: one fma per element
+                    __half a[4];
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) a[b] = __ldcs(Xh + (int64_t)rows[b] * D + c);
+                    const float cc = s_cen[c];
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) acc[b] = __fmaf_rn(__half2float(a[b]), cc, acc[b]);
+                }
             } else {
 #pragma unroll 2
                 for (int c = lane; c < D; c += 32) {                 // _shared.cuh:52-58: one fma per element
                     float a[4];
 #pragma unroll
-                    for (int b = 0; b < 4; ++b)
-                        a[b] = half_rows ? __half2float(__ldcs(reinterpret_cast<const __half*>(s.X) + (int64_t)rows[b] * D + c))
-                                         : __ldcs(s.X + (int64_t)rows[b] * D + c);
+                    for (int b = 0; b < 4; ++b) a[b] = __ldcs(s.X + (int64_t)rows[b] * D + c);
                     const float cc = s_cen[c];
 #pragma unroll
                     for (int b = 0; b < 4; ++b) acc[b] = __fmaf_rn(a[b], cc, acc[b]);

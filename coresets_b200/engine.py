@@ -107,7 +107,7 @@ _CELLS_MIN_ROWS = 1 << 18        # CELLS_MIN_ROWS: below this a full scan costs 
 _CELLS_PROBE_PICKS = 32          # CELLS_PROBE_PICKS: picks after a build before the visited share is read back
 _CELLS_GIVE_UP_SHARE = 0.2       # CELLS_GIVE_UP_SHARE: above this share of the slots per pick the scan kernel wins
 _CELLS_LIVE_GATE = 0.1           # CELLS_LIVE_GATE: no index while a pick still evaluates this share of the rows
-_HALF_RING_SHARE = 0.12         # HALF_RING_SHARE: float16 rows stay on the bulk-copy ring (2 bytes per element, every row)
+_HALF_RING_SHARE = 0.3          # HALF_RING_SHARE: float16 rows stay on the bulk-copy ring (2 bytes per element, every row)
                                  # while a pick still evaluates this share of them; 0 = never
 _EARLY_DENSE_PICKS = 24          # EARLY_DENSE_PICKS: nearly every row passes the triangle test this early, so
                                  # X is streamed with the bulk-copy ring
@@ -479,7 +479,7 @@ class ShardEngine:
         if n <= 0:
             return
         if self.half_ring and rules == RULE_NONE and self.n_host is not None and not self._ring_off:
-            # float16 rows: the ring while most rows are still evaluated (one read-back per stretch
+            # float16 rows: the ring while many rows are still evaluated (one read-back per stretch
             # of picks: 24, then every 25 % more), the pruned scan for the rest of the run
             while n > 0 and not self._ring_off:
                 cur = self.n_host
